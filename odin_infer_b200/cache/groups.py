@@ -1,17 +1,18 @@
 """Cache groups: storage for the layers that keep the same kind of thing.
 
 A mixer asks for what it keeps per sequence with a `KVRequest` (keys and
-values of `n_kv_heads` x `head_dim` per token, all of them or a window of the
-last `window`), or with state bytes of fixed size (see state.py).  Layers with
+values of `n_kv_heads` x `head_dim` per token, all of them, a window of the
+last `window`, or those of the current chunk of `chunk` positions), or with
+state bytes of fixed size.  Layers with
 equal requests share one group; every group has storage, a page pool and block
 tables of its own.
 
 Storage of one group: K and V as [line][page][kv head][PAGE tokens][head_dim],
 one "line" per schedule entry that writes to the group.  A sequence's pages are
 listed in its row of the block table, in order of position; page p of a row
-holds positions [p*PAGE, (p+1)*PAGE).  In a window group the pages that lie
-wholly before the window are given back as the sequence grows (their block
-table entries become -1).
+holds positions [p*PAGE, (p+1)*PAGE).  In a window or chunk group the pages
+that lie wholly before what the next query can see are given back as the
+sequence grows (their block table entries become -1).
 """
 from __future__ import annotations
 
@@ -30,10 +31,35 @@ class KVRequest:
     n_kv_heads: int
     head_dim: int
     window: int = 0  # 0: all keys; W > 0: the last W
+    chunk: int = 0   # C > 0: only the keys of the query's own chunk [floor(p / C) C, p]
+    v_head_dim: int = 0  # 0: as head_dim
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
     @property
     def key(self):
-        return ("kv", self.n_kv_heads, self.head_dim, self.window)
+        return ("kv", self.n_kv_heads, self.head_dim, self.window, self.chunk, self.value_dim)
+
+    def first_visible(self, position: int) -> int:
+        """The first key position that a query at `position` can see."""
+        first = 0
+        if self.window > 0:
+            first = max(first, position - self.window + 1)
+        if self.chunk > 0:
+            first = max(first, (position // self.chunk) * self.chunk)
+        return first
+
+    @staticmethod
+    def keeping_for_all(requests: list["KVRequest"]) -> "KVRequest":
+        """What a cache line must keep so that every one of `requests` (its writer and the
+        entries that read it, equal in geometry) finds its keys: their common mask if they
+        all have the same one, else everything."""
+        first = requests[0]
+        if all(r.window == first.window and r.chunk == first.chunk for r in requests):
+            return first
+        return KVRequest(first.n_kv_heads, first.head_dim, 0, 0, first.v_head_dim)
 
 
 def pages_for(n_tokens: int) -> int:
@@ -54,12 +80,17 @@ class KVGroup:
         self.v = None
 
     def storage_shape(self) -> tuple[int, ...]:
+        """Shape of the keys' storage (and of the values', when a value head has the keys' size)."""
         r = self.request
         return (self.n_lines, self.pool.n_pages, r.n_kv_heads, PAGE, r.head_dim)
 
+    def value_storage_shape(self) -> tuple[int, ...]:
+        r = self.request
+        return (self.n_lines, self.pool.n_pages, r.n_kv_heads, PAGE, r.value_dim)
+
     def bytes_per_token(self, itemsize: int) -> int:
         r = self.request
-        return 2 * self.n_lines * r.n_kv_heads * r.head_dim * itemsize
+        return self.n_lines * r.n_kv_heads * (r.head_dim + r.value_dim) * itemsize
 
     def attach_storage(self, k, v) -> None:
         self.k, self.v = k, v
@@ -74,12 +105,11 @@ class KVGroup:
             self.block_table[slot, have:need] = new_pages
 
     def release_before_window(self, slot: int, length: int) -> None:
-        """Window groups: give back the pages that no later token can see."""
-        w = self.request.window
-        if w <= 0:
+        """Window and chunk groups: give back the pages that no later token can see."""
+        if self.request.window <= 0 and self.request.chunk <= 0:
             return
-        # the next query sits at position `length`; it sees keys > length - w
-        first_needed = max(0, length - w + 1)
+        # the next query sits at position `length`; later queries see no earlier key than it does
+        first_needed = self.request.first_visible(length)
         first_page = first_needed // PAGE
         start = int(self.first_live_page[slot])
         if first_page > start:

@@ -12,6 +12,18 @@ from .groups import KVGroup, KVRequest, PAGE, pages_for
 from .pages import CacheError
 
 
+def _mask_probe_positions(a: KVRequest, b: KVRequest) -> list[int]:
+    """Positions at which two masks' first visible keys are compared: around every edge of either
+    mask within a few periods (the masks are periodic in their chunk and linear in their window)."""
+    edges = {0, 1}
+    for r in (a, b):
+        for size in (r.window, r.chunk):
+            if size > 0:
+                for m in range(1, 4):
+                    edges.update({m * size - 1, m * size, m * size + 1})
+    return sorted(e for e in edges if e >= 0)
+
+
 class CacheManager:
     def __init__(self, max_tokens: int, max_seq_len: int, max_slots: int | None = None):
         """max_tokens: the most tokens that live sequences hold together, each
@@ -47,7 +59,10 @@ class CacheManager:
             if not (0 <= shares_line_of < idx) or self.line_of[shares_line_of] is None:
                 raise CacheError(f"schedule entry {idx} reads the cache of entry {shares_line_of}, which keeps none")
             src_key, src_line = self.line_of[shares_line_of]
-            if kv is not None and kv.key != src_key:
+            kept = self.groups[src_key].request
+            if kv is not None and ((kv.n_kv_heads, kv.head_dim, kv.value_dim) != (kept.n_kv_heads, kept.head_dim, kept.value_dim)
+                                   or any(kept.first_visible(p) > kv.first_visible(p)
+                                          for p in _mask_probe_positions(kv, kept))):
                 raise CacheError(f"schedule entry {idx} cannot read the cache of entry {shares_line_of}: "
                                  f"it wants {kv.key}, the other keeps {src_key}")
             self.line_of.append((src_key, src_line))
@@ -128,7 +143,7 @@ class CacheManager:
         return old
 
     def after_step(self, slot: int) -> None:
-        """Called when a step's kernels are enqueued: window groups drop dead pages."""
+        """Called when a step's kernels are enqueued: window and chunk groups drop dead pages."""
         for g in self.groups.values():
             g.release_before_window(slot, self.lengths[slot])
 

@@ -1,5 +1,5 @@
-"""The one registry from an architecture's name (config.json "architectures"[0])
-to its configuration class and its model builder.
+"""The one registry from an architecture's name (config.json "architectures"[0], or
+the string under "architecture") to its configuration class and its model builder.
 
 Adding an architecture is one call of `register_architecture`: a subclass of
 ModelConfig that reads the architecture's own config.json keys, and a function
@@ -41,8 +41,11 @@ def lookup_architecture(name: str) -> Architecture:
 
 def config_from_dict(raw: dict, where: str = "config.json") -> ModelConfig:
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]
     if not (isinstance(archs, list) and archs and isinstance(archs[0], str)):
-        raise ConfigError(f"{where}: key 'architectures' must be a list that names the model class")
+        raise ConfigError(f"{where}: key 'architectures' must be a list that names the model class "
+                          "(or 'architecture' its name)")
     return lookup_architecture(archs[0]).config_class.from_dict(raw, where)
 
 

@@ -8,7 +8,11 @@
 // loop bound); softmax with the maximum subtracted (infer/ops.odin:21-37);
 // out = sum_t p_t v_t.  The softmax runs "online" over chunks of 32 keys that
 // start at the first visible key, so a token's result depends only on its own
-// sequence and position.  A window > 0 hides keys t <= pos - window.
+// sequence and position.  A window > 0 hides keys t <= pos - window; a chunk > 0 hides the
+// keys before the query's own chunk (position p sees t only if t / chunk == p / chunk, chunks
+// counted from the sequence's first position).  scale > 0 replaces 1 / sqrt(hd); softcap > 0
+// turns a score s into softcap * tanh(s / softcap) before the softmax.  A value head has vd
+// elements (keys and queries hd).
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -21,6 +25,10 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* _
 template <>
 __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, const float* __restrict__ k, int hd) {
     float acc = 0.f;
+    if (hd & 3) {  // rows that are not whole vectors: one element at a time
+        for (int i = 0; i < hd; ++i) acc = fmaf(q[i], k[i], acc);
+        return acc;
+    }
     const float4* k4 = reinterpret_cast<const float4*>(k);
     for (int i = 0; i < hd / 4; ++i) {
         const float4 v = k4[i];
@@ -35,6 +43,10 @@ __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, con
 template <>
 __device__ __forceinline__ float dot_row<bf16>(const float* __restrict__ q, const bf16* __restrict__ k, int hd) {
     float acc = 0.f;
+    if (hd & 7) {  // rows that are not whole vectors: one element at a time
+        for (int i = 0; i < hd; ++i) acc = fmaf(q[i], __bfloat162float(k[i]), acc);
+        return acc;
+    }
     const uint4* k8 = reinterpret_cast<const uint4*>(k);
     for (int i = 0; i < hd / 8; ++i) {
         const uint4 v = k8[i];
@@ -52,9 +64,10 @@ __device__ __forceinline__ float dot_row<bf16>(const float* __restrict__ q, cons
 template <typename T>
 __global__ void __launch_bounds__(AP_WARPS * 32)
 attention_plain_kernel(const T* __restrict__ q, size_t q_stride, T* __restrict__ out, size_t out_stride, int T_tok,
-                       int Hq, int Hkv, int hd, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                       int Hq, int Hkv, int hd, int vd, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                        int page_size, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
-                       const int* __restrict__ block_table, int bt_stride, int window) {
+                       const int* __restrict__ block_table, int bt_stride, int window, int chunk, float scale,
+                       float softcap) {
     __shared__ float qs[AP_WARPS][AP_MAX_HD];
     pdl_trigger();
     pdl_wait();
@@ -74,6 +87,7 @@ attention_plain_kernel(const T* __restrict__ q, size_t q_stride, T* __restrict__
     const float inv_scale = sqrtf((float)hd);
     int t_lo = 0;
     if (window > 0 && pos - window + 1 > 0) t_lo = pos - window + 1;
+    if (chunk > 0) t_lo = max(t_lo, (pos / chunk) * chunk);
 
     float m = -CUDART_INF_F, l = 0.f;
     float acc[AP_MAX_HD / 32];
@@ -90,7 +104,9 @@ attention_plain_kernel(const T* __restrict__ q, size_t q_stride, T* __restrict__
             const int page = bt[tk / page_size];
             if (page >= 0) {
                 row = ((long long)page * Hkv + kvh) * page_size + (tk % page_size);
-                s = dot_row<T>(qf, k_cache + (size_t)row * hd, hd) / inv_scale;
+                const float dot = dot_row<T>(qf, k_cache + (size_t)row * hd, hd);
+                s = scale > 0.f ? dot * scale : dot / inv_scale;
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -106,43 +122,47 @@ attention_plain_kernel(const T* __restrict__ q, size_t q_stride, T* __restrict__
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const long long rj = __shfl_sync(0xffffffffu, row, j);
             if (rj < 0) continue;
-            const T* vrow = v_cache + (size_t)rj * hd;
+            const T* vrow = v_cache + (size_t)rj * vd;
 #pragma unroll
             for (int r = 0; r < AP_MAX_HD / 32; ++r) {
                 const int d = r * 32 + lane;
-                if (d < hd) acc[r] = fmaf(pj, to_f32(vrow[d]), acc[r]);
+                if (d < vd) acc[r] = fmaf(pj, to_f32(vrow[d]), acc[r]);
             }
         }
     }
-    T* orow = out + (size_t)t * out_stride + (size_t)h * hd;
+    T* orow = out + (size_t)t * out_stride + (size_t)h * vd;
     const float inv_l = (l > 0.f) ? 1.0f / l : 0.f;
 #pragma unroll
     for (int r = 0; r < AP_MAX_HD / 32; ++r) {
         const int d = r * 32 + lane;
-        if (d < hd) orow[d] = from_f32<T>(acc[r] * inv_l);
+        if (d < vd) orow[d] = from_f32<T>(acc[r] * inv_l);
     }
 }
 
-// q: [T, Hq*hd] with row stride q_row_stride (elements); out likewise.
+// q: [T, Hq*hd] with row stride q_row_stride (elements); out: [T, Hq*vd] with row stride out_row_stride.
 extern "C" int odin_attention_plain(const void* q, long long q_row_stride, void* out, long long out_row_stride,
-                                    int dtype, int T, int Hq, int Hkv, int hd, const void* k_cache,
+                                    int dtype, int T, int Hq, int Hkv, int hd, int vd, const void* k_cache,
                                     const void* v_cache, int page_size, const int* tok_pos, const int* tok_seq,
-                                    const int* block_table, int bt_stride, int window, void* stream) {
+                                    const int* block_table, int bt_stride, int window, int chunk, float scale,
+                                    float softcap, void* stream) {
     if (T <= 0) return 0;
-    if (hd <= 0 || hd > AP_MAX_HD || (hd % 8) != 0 || Hkv <= 0 || Hq % Hkv != 0) return ODIN_ERR_UNSUPPORTED;
+    if (hd <= 0 || hd > AP_MAX_HD || vd <= 0 || vd > AP_MAX_HD || Hkv <= 0 || Hq % Hkv != 0 ||
+        window < 0 || chunk < 0)
+        return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const long long items = (long long)T * Hq;
     const long long blocks = (items + AP_WARPS - 1) / AP_WARPS;
     if (blocks > 2147483647LL) return ODIN_ERR_UNSUPPORTED;
     if (dtype == ODIN_BF16)
         odin_launch(attention_plain_kernel<bf16>, dim3((unsigned)blocks), dim3(AP_WARPS * 32), 0, s,
-            (const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, T, Hq, Hkv, hd,
-            (const bf16*)k_cache, (const bf16*)v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride, window);
+            (const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, T, Hq, Hkv, hd, vd,
+            (const bf16*)k_cache, (const bf16*)v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride, window,
+            chunk, scale, softcap);
     else if (dtype == ODIN_F32)
         odin_launch(attention_plain_kernel<float>, dim3((unsigned)blocks), dim3(AP_WARPS * 32), 0, s,
-            (const float*)q, (size_t)q_row_stride, (float*)out, (size_t)out_row_stride, T, Hq, Hkv, hd,
+            (const float*)q, (size_t)q_row_stride, (float*)out, (size_t)out_row_stride, T, Hq, Hkv, hd, vd,
             (const float*)k_cache, (const float*)v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride,
-            window);
+            window, chunk, scale, softcap);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();

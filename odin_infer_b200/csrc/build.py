@@ -27,6 +27,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # group -> sources; every group also depends on every header of this folder
 GROUPS = {
     "elementwise": ["elementwise.cu"],
+    "rowwise": ["rowwise.cu"],
+    "recurrent": ["recurrent.cu"],
     "gemm_plain": ["gemm_plain.cu"],
     "head_prep": ["head_prep.cu"],
     "attention_plain": ["attention_plain.cu"],

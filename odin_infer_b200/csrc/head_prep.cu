@@ -18,11 +18,14 @@
 
 // TI: element type of the projection (bfloat16 or 32-bit; n_split 32-bit partial sums of a
 // split product are added first, in order).  T: element type of q_out and of the cache.
+// bias: one value per column of the projection, added first (null: none).  norm_mode 0: no norm;
+// 1: RMSNorm with a weight before the rotation; 2: division by the root mean square after the
+// rotation, no weight.  vd: size of a value head (key and query heads have hd).
 template <typename TI, typename T>
 __global__ void __launch_bounds__(HP_WARPS * 32)
 head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // may alias: no restrict
-                 size_t q_out_stride, int Hq, int Hkv, int hd, size_t row_stride, VecRef qw, VecRef kw,
-                 int has_norm, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                 size_t q_out_stride, int Hq, int Hkv, int hd, int vd, size_t row_stride, VecRef bias, VecRef qw,
+                 VecRef kw, int norm_mode, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                  int rot, int table_len, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                  const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_cache,
                  T* __restrict__ v_cache, int page_size, int write_kv) {
@@ -37,34 +40,38 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
     const int seq = tok_seq[t];
     if (seq < 0) return;  // padding token
     const int pos = tok_pos[t];
-    const TI* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
 
     const bool is_q = head < Hq;
     const bool is_k = !is_q && head < Hq + Hkv;
     const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hkv);
     if (!is_q && !write_kv) return;
+    const bool is_v = !is_q && !is_k;
+    const int n = is_v ? vd : hd;  // this head's size
+    const size_t col0 = is_v ? (size_t)(Hq + Hkv) * hd + (size_t)kvh * vd : (size_t)head * hd;
+    const TI* src = qkv + (size_t)t * row_stride + col0;
 
     T* dst = q_out + (size_t)t * q_out_stride + (size_t)head * hd;
     if (!is_q) {
         const int page = block_table[(size_t)seq * bt_stride + pos / page_size];
         if (page < 0) return;
         T* base = is_k ? k_cache : v_cache;
-        dst = base + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * hd;
+        dst = base + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * n;
     }
 
     float* b = buf[warp];
     float ss = 0.f;
-    for (int j = lane; j < hd; j += 32) {
+    for (int j = lane; j < n; j += 32) {
         float v = to_f32(src[j]);
         for (int sp = 1; sp < n_split; ++sp) v += to_f32(src[(size_t)sp * split_stride + j]);
+        if (bias.p != nullptr) v += bias.at((int)col0 + j);
         b[j] = v;
         ss += v * v;
     }
-    if (!is_q && !is_k) {  // value head: stored as it is
-        for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(b[j]);
+    if (is_v) {  // value head: stored as it is
+        for (int j = lane; j < n; j += 32) dst[j] = from_f32<T>(b[j]);
         return;
     }
-    if (has_norm) {
+    if (norm_mode == 1) {
         ss = warp_sum(ss);
         ss /= (float)hd;
         ss += eps;
@@ -75,17 +82,34 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
     __syncwarp();
     const int half = rot >> 1;
     const bool in_table = (pos >= 0 && pos < table_len);
-    for (int j = lane; j < hd; j += 32) {
-        float o;
+    float o[HP_MAX_HD / 32];
+    float s2 = 0.f;
+#pragma unroll
+    for (int e = 0; e < HP_MAX_HD / 32; ++e) {
+        const int j = lane + 32 * e;
+        if (j >= hd) break;
         if (j < rot && in_table) {
             const int i = (j < half) ? j : j - half;
             const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
             const float x = b[i], y = b[i + half];
-            o = (j < half) ? (x * c - y * s) : (x * s + y * c);
+            o[e] = (j < half) ? (x * c - y * s) : (x * s + y * c);
         } else {
-            o = b[j];
+            o[e] = b[j];
         }
-        dst[j] = from_f32<T>(o);
+        s2 += o[e] * o[e];
+    }
+    float r2 = 1.0f;
+    if (norm_mode == 2) {
+        s2 = warp_sum(s2);
+        s2 /= (float)hd;
+        s2 += eps;
+        r2 = 1.0f / sqrtf(s2);
+    }
+#pragma unroll
+    for (int e = 0; e < HP_MAX_HD / 32; ++e) {
+        const int j = lane + 32 * e;
+        if (j >= hd) break;
+        dst[j] = from_f32<T>(norm_mode == 2 ? o[e] * r2 : o[e]);
     }
 }
 
@@ -247,21 +271,29 @@ head_prep_token_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_
 // qkv: [n_split][T, (Hq + 2 Hkv) hd] of in_dtype (row stride row_stride, parts split_stride
 // elements apart).  q_out: [T, Hq hd] of dtype (row stride q_out_stride); it may be qkv
 // itself when there is one part of the same type (q is then normalised and rotated in place).
+// bias (null: none), norm_mode and vd as the general kernel describes them; the fast kernels take no
+// bias, norm_mode 0 or 1 and vd == hd.
 extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long long split_stride, void* q_out,
-                              long long q_out_stride, int dtype, int T, int Hq, int Hkv, int hd, long long row_stride,
-                              const void* q_norm_w, const void* k_norm_w, int w_dtype, int has_norm, float eps,
+                              long long q_out_stride, int dtype, int T, int Hq, int Hkv, int hd, int vd,
+                              long long row_stride, const void* bias, int bias_dtype, const void* q_norm_w,
+                              const void* k_norm_w, int w_dtype, int norm_mode, float eps,
                               const float* cos_t, const float* sin_t, int rot, int table_len,
                               const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
                               void* k_cache, void* v_cache, int page_size, int write_kv, void* stream) {
     if (T <= 0) return 0;
-    if (hd > HP_MAX_HD || hd <= 0 || (rot & 1) || rot > hd || rot < 0 || n_split < 1) return ODIN_ERR_UNSUPPORTED;
+    if (hd > HP_MAX_HD || hd <= 0 || vd > HP_MAX_HD || vd <= 0 || (rot & 1) || rot > hd || rot < 0 || n_split < 1 ||
+        norm_mode < 0 || norm_mode > 2)
+        return ODIN_ERR_UNSUPPORTED;
+    const int has_norm = norm_mode == 1;
+    const bool plain_heads = bias == nullptr && norm_mode != 2 && vd == hd;
     cudaStream_t s = (cudaStream_t)stream;
     const int n_heads = Hq + 2 * Hkv;
     dim3 grid(T, (n_heads + HP_WARPS - 1) / HP_WARPS);
     if (grid.y > 65535) return ODIN_ERR_UNSUPPORTED;
     VecRef qw{q_norm_w, w_dtype == ODIN_BF16}, kw{k_norm_w, w_dtype == ODIN_BF16};
+    VecRef bv{bias, bias_dtype == ODIN_BF16};
     const bool fast_in = (in_dtype == ODIN_BF16 && n_split == 1) || in_dtype == ODIN_F32;
-    if (fast_in && dtype == ODIN_BF16 && rot == hd && (hd == 64 || hd == 128) && (row_stride % 4) == 0 &&
+    if (plain_heads && fast_in && dtype == ODIN_BF16 && rot == hd && (hd == 64 || hd == 128) && (row_stride % 4) == 0 &&
         (split_stride % 4) == 0 && (q_out_stride % 4) == 0 &&
         ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)cos_t) | ((uintptr_t)sin_t)) & 15) == 0) {
 #define FAST(VEC, TI, TOK)                                                                                         \
@@ -289,8 +321,8 @@ extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long l
     }
 #define GO(TI, TT)                                                                                                  \
     odin_launch(head_prep_kernel<TI, TT>, grid, dim3(HP_WARPS * 32), 0, s,                                           \
-        (const TI*)qkv, n_split, (size_t)split_stride, (TT*)q_out, (size_t)q_out_stride, Hq, Hkv, hd,               \
-        (size_t)row_stride, qw, kw, has_norm, eps, cos_t, sin_t, rot, table_len, tok_pos, tok_seq, block_table,     \
+        (const TI*)qkv, n_split, (size_t)split_stride, (TT*)q_out, (size_t)q_out_stride, Hq, Hkv, hd, vd,           \
+        (size_t)row_stride, bv, qw, kw, norm_mode, eps, cos_t, sin_t, rot, table_len, tok_pos, tok_seq, block_table,     \
         (int)bt_stride, (TT*)k_cache, (TT*)v_cache, page_size, write_kv)
     if (in_dtype == ODIN_BF16 && dtype == ODIN_BF16) GO(bf16, bf16);
     else if (in_dtype == ODIN_F32 && dtype == ODIN_F32) GO(float, float);

@@ -140,6 +140,146 @@ def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
         c_longlong(src.numel()), _stream()), "cast")
 
 
+ACTIVATIONS = {"tanh": 0, "silu": 1, "gelu_tanh": 2, "xielu": 3}
+
+
+def _parts(t: torch.Tensor, rows: int, cols: int) -> tuple[int, int]:
+    """(number of partial sums, their distance in elements) of a product's output [rows, cols] or [parts, rows, cols]."""
+    assert t.is_contiguous() and tuple(t.shape[-2:]) == (rows, cols)
+    return (t.shape[0], rows * cols) if t.dim() == 3 else (1, 0)
+
+
+def row_update(x: torch.Tensor, delta: torch.Tensor | None, bias: torch.Tensor | None, weight: torch.Tensor | None,
+               eps: float, groups: int, out: torch.Tensor | None, rows: torch.Tensor | None = None,
+               normalise: bool = True) -> None:
+    """x += sum of delta's parts + bias (in place, 32-bit; not with a row gather), then
+    normalise: out = weight * x / rms, the root mean square taken over each of `groups` equal
+    consecutive parts of the row by itself (out may be x: in place); else out = x converted
+    (out None: the update alone)."""
+    d = x.shape[-1]
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    n_split, stride = (1, 0)
+    if delta is not None:
+        n_split, stride = _parts(delta, x.shape[0], d)
+    if out is not None:
+        assert out.is_contiguous() and out.shape[-1] == d
+    n_rows = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        assert rows.dtype == torch.int32 and out is not None and out.shape[0] == n_rows
+    if normalise:
+        assert weight is not None and weight.numel() == d and out is not None and d % groups == 0
+    if bias is not None:
+        assert bias.numel() == d
+    _check(_fn("rowwise", "odin_row_update")(
+        _ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype) if delta is not None else 0), c_int(n_split),
+        c_longlong(stride), _ptr(bias), c_int(dtype_code(bias.dtype) if bias is not None else 0), _ptr(weight),
+        c_int(dtype_code(weight.dtype) if weight is not None else 0), c_float(eps), c_int(groups),
+        c_int(0 if normalise else 1), _ptr(out), c_int(dtype_code(out.dtype) if out is not None else 0), _ptr(rows),
+        c_int(n_rows), c_int(d), _stream()), "row_update")
+
+
+def normed_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, tok_seq: torch.Tensor | None = None) -> None:
+    """x += weight * y / rms(y) row by row; y may be [parts, n, d] partial sums.  Rows of sequence -1 are skipped."""
+    n, d = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and weight.numel() == d
+    n_split, stride = _parts(y, n, d)
+    _check(_fn("rowwise", "odin_normed_add")(
+        _ptr(x), _ptr(y), c_int(dtype_code(y.dtype)), c_int(n_split), c_longlong(stride), _ptr(weight),
+        c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(tok_seq), c_int(n), c_int(d), _stream()), "normed_add")
+
+
+def activation(src: torch.Tensor, kind: str, out: torch.Tensor, params: torch.Tensor | None = None) -> None:
+    """out = act(src) element by element; src [T, n] (a strided view is fine) or [parts, T, n] partial sums,
+    added first.  kind: tanh, silu, gelu_tanh, or xielu with params = (p, q):
+    z > 0: softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (e^z - 1 - z) + z/2."""
+    T, n = out.shape
+    assert out.stride(1) == 1 and src.stride(-1) == 1 and tuple(src.shape[-2:]) == (T, n)
+    if src.dim() == 3:
+        assert src.is_contiguous()
+        n_split, stride, row = src.shape[0], T * n, n
+    else:
+        n_split, stride, row = 1, 0, src.stride(0)
+    _check(_fn("rowwise", "odin_activation")(
+        _ptr(src), c_int(dtype_code(src.dtype)), c_int(n_split), c_longlong(stride), c_longlong(row),
+        c_int(ACTIVATIONS[kind]), _ptr(params), c_int(dtype_code(params.dtype) if params is not None else 0), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), c_int(T), c_int(n), _stream()), "activation")
+
+
+def gated_lookup(gate: torch.Tensor, kind: str, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, c] = act(gate[t, c]) * table[ids[t], col0 + c]; gate may be [parts, T, n] partial sums."""
+    T, n = out.shape
+    assert out.is_contiguous() and table.stride(1) == 1 and ids.dtype == torch.int32 and col0 + n <= table.shape[1]
+    n_split, stride = _parts(gate, T, n)
+    _check(_fn("rowwise", "odin_gated_lookup")(
+        _ptr(gate), c_int(dtype_code(gate.dtype)), c_int(n_split), c_longlong(stride), c_int(ACTIVATIONS[kind]),
+        _ptr(table), c_int(dtype_code(table.dtype)), c_longlong(table.stride(0)), c_int(col0), c_int(table.shape[0]),
+        _ptr(ids), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(n), _stream()), "gated_lookup")
+
+
+def token_shift(h: torch.Tensor, state: torch.Tensor, mu: torch.Tensor, out: torch.Tensor, tok_seq: torch.Tensor,
+                seq_start: torch.Tensor, seq_slots: torch.Tensor) -> None:
+    """out[s, t] = h[t] + (before - h[t]) * mu[s]: `before` is the row above in the same sequence or, for a
+    sequence's first row of this step, the row of `state` (float32 [slots, >= d], any row stride) of its slot."""
+    T, d = h.shape
+    n_mix = mu.shape[0]
+    assert h.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (n_mix, T, d) and out.dtype == h.dtype
+    assert mu.is_contiguous() and mu.shape[1] == d and state.dtype == torch.float32 and state.stride(1) == 1
+    _check(_fn("recurrent", "odin_token_shift")(
+        _ptr(h), c_int(dtype_code(h.dtype)), _ptr(state), c_longlong(state.stride(0)), _ptr(mu),
+        c_int(dtype_code(mu.dtype)), c_int(n_mix), _ptr(out), _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slots),
+        c_int(T), c_int(d), _stream()), "token_shift")
+
+
+RECURRENCE_MODES = {"bonus": 0, "gated": 1}
+
+
+def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: torch.Tensor, v: torch.Tensor,
+                      c0: torch.Tensor, c1: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
+                      seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int, n_heads: int, dk: int, dv: int,
+                      shift_src: torch.Tensor | None = None, shift_state: torch.Tensor | None = None) -> None:
+    """The recurrence over a matrix-valued state per (sequence, head), S: [dk, dv] in `state`
+    (float32 [slots, >= H dk dv], any row stride), sequence b's rows being seq_start[b] .. seq_start[b+1]:
+
+    "bonus": w = exp(-exp(g + c0)); o = (S + diag(c1) k v^T)^T q; S = diag(w) S + k v^T
+    "gated": f = c1 + (1 - c1) sigmoid(g + c0); S = diag(f) S + (1 - f) v^T; o = S^T silu(q)
+
+    q, k, g: float32 [T, H dk] (strided views are fine), v, out: float32 [T, H dv].
+    shift_src / shift_state: after the walk the last row of shift_src of every sequence is stored
+    (as float32) in its slot's row of shift_state."""
+    for t in (q, g, v, out) + ((k,) if k is not None else ()):
+        assert t.dtype == torch.float32 and t.stride(1) == 1
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and c0.dtype == c1.dtype
+    assert c0.numel() == n_heads * dk and c1.numel() == n_heads * dk
+    kk = k if k is not None else q
+    width = 0
+    if shift_src is not None:
+        assert shift_state is not None and shift_src.is_contiguous() and shift_state.dtype == torch.float32
+        width = shift_src.shape[1]
+    _check(_fn("recurrent", "odin_linear_recurrence")(
+        c_int(RECURRENCE_MODES[mode]), _ptr(q), c_longlong(q.stride(0)), _ptr(kk), c_longlong(kk.stride(0)),
+        _ptr(g), c_longlong(g.stride(0)), _ptr(v), c_longlong(v.stride(0)), _ptr(c0), _ptr(c1),
+        c_int(dtype_code(c0.dtype)), _ptr(out), c_longlong(out.stride(0)), _ptr(state), c_longlong(state.stride(0)),
+        _ptr(seq_start), _ptr(seq_slots), c_int(n_seqs), c_int(n_heads), c_int(dk), c_int(dv), _ptr(shift_src),
+        c_int(dtype_code(shift_src.dtype) if shift_src is not None else 0), _ptr(shift_state),
+        c_longlong(shift_state.stride(0) if shift_state is not None else 0), c_int(width), _stream()),
+        "linear_recurrence")
+
+
+def head_unit_scale(o: torch.Tensor, weight: torch.Tensor, per_head_weight: bool, gate: torch.Tensor | None,
+                    eps: float, out: torch.Tensor, n_heads: int, dv: int) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]) per head of dv elements; weight is
+    [H dv] (per_head_weight) or [dv] shared by the heads; gate (float32, optional) may be a strided view."""
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (T, n_heads * dv)
+    assert weight.numel() == (n_heads * dv if per_head_weight else dv)
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1
+    _check(_fn("recurrent", "odin_head_unit_scale")(
+        _ptr(o), _ptr(weight), c_int(dtype_code(weight.dtype)), c_int(dv if per_head_weight else 0), _ptr(gate),
+        c_longlong(gate.stride(0) if gate is not None else 0), c_float(eps), _ptr(out), c_int(dtype_code(out.dtype)),
+        c_int(T), c_int(n_heads), c_int(dv), _stream()), "head_unit_scale")
+
+
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores with 32-bit accumulation."""
     M, K = a.shape
@@ -283,13 +423,19 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
               k_norm: torch.Tensor | None, eps: float, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int,
               tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
               k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, write_kv: bool = True,
-              q_out: torch.Tensor | None = None) -> torch.Tensor:
+              q_out: torch.Tensor | None = None, bias: torch.Tensor | None = None, unit_norm_after: bool = False,
+              v_head_dim: int | None = None) -> torch.Tensor:
     """Per-head RMSNorm and rotation of q and k, and the cache write of k and v.
+
+    bias: one value per column of the projection, added first.  unit_norm_after: instead of the
+    weighted norm before the rotation, q and k heads are divided by their root mean square after it
+    (q_norm and k_norm are then None).  v_head_dim: size of a value head when it differs from head_dim.
 
     qkv: [T, (n_q + 2 n_kv) head_dim], or float32 partial sums [parts, T, ...] of a split
     product (added first).  q goes to q_out ([T, n_q head_dim], of the cache's type); without
     q_out it is written back into qkv (one part only).  Returns the tensor that holds q."""
-    width = (n_q + 2 * n_kv) * head_dim
+    vd = head_dim if v_head_dim is None else v_head_dim
+    width = (n_q + n_kv) * head_dim + n_kv * vd
     if qkv.dim() == 3:
         n_split, T = qkv.shape[0], qkv.shape[1]
         assert qkv.is_contiguous() and qkv.shape[2] == width
@@ -305,18 +451,23 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
     assert tok_pos.dtype == torch.int32 and tok_seq.dtype == torch.int32 and block_table.dtype == torch.int32
     has_norm = q_norm is not None
     if has_norm:
-        assert k_norm is not None and q_norm.dtype == k_norm.dtype
+        assert k_norm is not None and q_norm.dtype == k_norm.dtype and not unit_norm_after
         assert q_norm.numel() == head_dim and k_norm.numel() == head_dim
+    if bias is not None:
+        assert bias.numel() == width and bias.is_contiguous()
     if write_kv:
         assert k_cache is not None and v_cache is not None
         assert k_cache.dtype == q_out.dtype and v_cache.dtype == q_out.dtype
         assert k_cache.is_contiguous() and v_cache.is_contiguous()
         assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim), "cache layout is [page][kv head][64][hd]"
+        assert tuple(v_cache.shape[1:]) == (n_kv, PAGE, vd), "value cache layout is [page][kv head][64][vd]"
     _check(_fn("head_prep", "odin_head_prep")(
         _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(n_split), c_longlong(split_stride), _ptr(q_out),
         c_longlong(q_out.stride(0)), c_int(dtype_code(q_out.dtype)), c_int(T), c_int(n_q), c_int(n_kv),
-        c_int(head_dim), c_longlong(row_stride), _ptr(q_norm), _ptr(k_norm),
-        c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(1 if has_norm else 0), c_float(eps),
+        c_int(head_dim), c_int(vd), c_longlong(row_stride), _ptr(bias),
+        c_int(dtype_code(bias.dtype) if bias is not None else 0), _ptr(q_norm), _ptr(k_norm),
+        c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(2 if unit_norm_after else (1 if has_norm else 0)),
+        c_float(eps),
         _ptr(cos), _ptr(sin), c_int(rotary_dim), c_int(cos.shape[0]), _ptr(tok_pos), _ptr(tok_seq),
         _ptr(block_table), c_int(block_table.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
         c_int(1 if write_kv else 0), _stream()), "head_prep")
@@ -325,17 +476,24 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                     k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
-                    block_table: torch.Tensor, window: int = 0) -> None:
-    """Causal attention of each token over its sequence's cache; q may be a strided view."""
+                    block_table: torch.Tensor, window: int = 0, chunk: int = 0, scale: float = 0.0,
+                    softcap: float = 0.0, v_head_dim: int | None = None) -> None:
+    """Causal attention of each token over its sequence's cache; q may be a strided view.
+
+    window > 0: only the last `window` keys; chunk > 0: only the keys of the query's own chunk of
+    `chunk` positions; scale > 0 replaces 1 / sqrt(head_dim); softcap > 0: scores pass through
+    softcap * tanh(score / softcap); v_head_dim: size of a value head when it differs."""
     T = q.shape[0]
+    vd = head_dim if v_head_dim is None else v_head_dim
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype
-    assert q.shape[1] == n_q * head_dim and out.shape == (T, n_q * head_dim)
+    assert q.shape[1] == n_q * head_dim and out.shape == (T, n_q * vd)
     assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim) and k_cache.is_contiguous()
+    assert tuple(v_cache.shape[1:]) == (n_kv, PAGE, vd) and v_cache.is_contiguous()
     _check(_fn("attention_plain", "odin_attention_plain")(
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(dtype_code(q.dtype)),
-        c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
-        _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window),
-        _stream()), "attention_plain")
+        c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(vd), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
+        _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window), c_int(chunk),
+        c_float(scale), c_float(softcap), _stream()), "attention_plain")
 
 
 def attention_decode_supported(head_dim: int) -> bool:

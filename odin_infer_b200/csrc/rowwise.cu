@@ -1,0 +1,260 @@
+// Row kernels of the layers that are not plain RMSNorm + SwiGLU:
+//   * the residual update with a norm in groups (the row is cut into equal consecutive parts,
+//     each divided by its own root mean square), an optional bias on the update, and the
+//     result either normalised (into another buffer or in place) or merely converted;
+//   * x += w * (y / rms(y)): an update that is normalised before it is added;
+//   * element-wise activations of a product's output (tanh, SiLU, tanh-GELU, xIELU), which add
+//     the partial sums of a split product first;
+//   * a gate times a row of a per-token table (the product of a gate with a slice of a second
+//     embedding).
+// All arithmetic is 32-bit; a row's sums run in an order fixed by the block size alone, so a
+// row's result does not depend on the other rows of the launch.
+#include "common.cuh"
+
+#define ROW_THREADS 256
+
+// ------------------------------------------------------------ residual update + grouped norm
+// x_new = x + sum_s delta[s] + bias.  It is written back to x when there is an update and no
+// row gather.  mode 0: out = w * (x_new / sqrt(mean_g(x_new^2) + eps)) with the mean over the
+// element's own group; out may be x itself (32-bit, in place).  mode 1: out = x_new converted
+// (out may be null: the update alone).
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(ROW_THREADS)
+row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t split_stride, VecRef bias, VecRef w,
+                  float eps, int groups, int mode, TO* out, const int* __restrict__ rows, int d) {
+    __shared__ float red[32];
+    extern __shared__ float rowbuf[];  // d floats
+    pdl_trigger();
+    const int r = blockIdx.x;
+    int src = r;
+    if (rows != nullptr) src = rows[r];
+    pdl_wait();
+    TO* o = out == nullptr ? nullptr : out + (size_t)r * d;
+    if (src < 0) {
+        if (o != nullptr && (void*)out != (void*)x)
+            for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = from_f32<TO>(0.f);
+        return;
+    }
+    float* xr = x + (size_t)src * d;
+    const bool updated = delta != nullptr || bias.p != nullptr;
+    const bool write_back = updated && rows == nullptr;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = xr[j];
+        if (delta != nullptr)
+            for (int s = 0; s < n_split; ++s) v += to_f32(delta[(size_t)s * split_stride + (size_t)src * d + j]);
+        if (bias.p != nullptr) v += bias.at(j);
+        rowbuf[j] = v;
+    }
+    __syncthreads();
+    if (mode == 1) {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            const float v = rowbuf[j];
+            if (write_back) xr[j] = v;
+            if (o != nullptr) o[j] = from_f32<TO>(v);
+        }
+        return;
+    }
+    const int gsz = d / groups;
+    for (int g = 0; g < groups; ++g) {
+        float ss = 0.f;
+        for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
+            const float v = rowbuf[g * gsz + j];
+            ss += v * v;
+        }
+        ss = block_sum(ss, red);
+        ss /= (float)gsz;
+        ss += eps;
+        const float rs = 1.0f / sqrtf(ss);
+        for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
+            const int c = g * gsz + j;
+            const float v = rowbuf[c];
+            if (write_back && (void*)out != (void*)x) xr[c] = v;
+            o[c] = from_f32<TO>(w.at(c) * (rs * v));
+        }
+    }
+}
+
+extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
+                               const void* bias, int bias_dtype, const void* w, int w_dtype, float eps, int groups,
+                               int mode, void* out, int out_dtype, const int* rows, int n_rows, int d, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0 || (mode != 0 && mode != 1)) return ODIN_ERR_BAD_ARG;
+    if (mode == 0 && (groups <= 0 || d % groups != 0 || w == nullptr || out == nullptr)) return ODIN_ERR_BAD_ARG;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    VecRef wv{w, w_dtype == ODIN_BF16}, bv{bias, bias_dtype == ODIN_BF16};
+#define GO(TD, TO)                                                                                               \
+    do {                                                                                                         \
+        auto kern = row_update_kernel<TD, TO>;                                                                   \
+        if (smem > 48 * 1024) {                                                                                  \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+            if (e != cudaSuccess) return (int)e;                                                                 \
+        }                                                                                                        \
+        odin_launch(kern, dim3(n_rows), dim3(ROW_THREADS), smem, s, x, (const TD*)delta, n_split,                 \
+                    (size_t)split_stride, bv, wv, eps, groups, mode, (TO*)out, rows, d);                         \
+    } while (0)
+    const bool dbf = delta != nullptr && delta_dtype == ODIN_BF16;
+    if (out_dtype == ODIN_BF16) { if (dbf) GO(bf16, bf16); else GO(float, bf16); }
+    else if (out_dtype == ODIN_F32) { if (dbf) GO(bf16, float); else GO(float, float); }
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ x += w * (y / rms(y))
+template <typename TY>
+__global__ void __launch_bounds__(ROW_THREADS)
+normed_add_kernel(float* __restrict__ x, const TY* __restrict__ y, int n_split, size_t split_stride, VecRef w, float eps,
+                  const int* __restrict__ tok_seq, int d) {
+    __shared__ float red[32];
+    extern __shared__ float rowbuf[];
+    pdl_trigger();
+    const int r = blockIdx.x;
+    pdl_wait();
+    if (tok_seq != nullptr && tok_seq[r] < 0) return;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < n_split; ++s) v += to_f32(y[(size_t)s * split_stride + (size_t)r * d + j]);
+        rowbuf[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    ss /= (float)d;
+    ss += eps;
+    const float rs = 1.0f / sqrtf(ss);
+    float* xr = x + (size_t)r * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) xr[j] += w.at(j) * (rs * rowbuf[j]);
+}
+
+extern "C" int odin_normed_add(float* x, const void* y, int y_dtype, int n_split, long long split_stride, const void* w,
+                               int w_dtype, float eps, const int* tok_seq, int n_rows, int d, void* stream) {
+    if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (d <= 0 || smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    VecRef wv{w, w_dtype == ODIN_BF16};
+#define GO(TY)                                                                                                   \
+    do {                                                                                                         \
+        auto kern = normed_add_kernel<TY>;                                                                       \
+        if (smem > 48 * 1024) {                                                                                  \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+            if (e != cudaSuccess) return (int)e;                                                                 \
+        }                                                                                                        \
+        odin_launch(kern, dim3(n_rows), dim3(ROW_THREADS), smem, s, x, (const TY*)y, n_split, (size_t)split_stride, \
+                    wv, eps, tok_seq, d);                                                                        \
+    } while (0)
+    if (y_dtype == ODIN_BF16) GO(bf16);
+    else if (y_dtype == ODIN_F32) GO(float);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ activations
+#define ACT_TANH 0
+#define ACT_SILU 1
+#define ACT_GELU_TANH 2
+#define ACT_XIELU 3
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// xIELU with a_p = softplus(p), a_n = 1/2 + softplus(q):
+//   z > 0: a_p z^2 + z/2;   z <= 0: a_n (e^z - 1 - z) + z/2
+__device__ __forceinline__ float activate(int act, float z, float c0, float c1) {
+    switch (act) {
+        case ACT_TANH: return tanhf(z);
+        case ACT_SILU: return z / (1.0f + expf(-z));
+        case ACT_GELU_TANH: return gelu_tanh_f(z);
+        default: return z > 0.f ? c0 * z * z + 0.5f * z : c1 * (expm1f(z) - z) + 0.5f * z;
+    }
+}
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+activation_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, size_t in_stride, int act, VecRef params,
+                  TO* __restrict__ out, size_t out_stride, int T, int n) {
+    pdl_trigger();
+    float c0 = 0.f, c1 = 0.f;
+    if (act == ACT_XIELU) {
+        c0 = softplus_f(params.at(0));
+        c1 = 0.5f + softplus_f(params.at(1));
+    }
+    pdl_wait();
+    const long long total = (long long)T * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / n), c = (int)(i % n);
+        float z = 0.f;
+        for (int s = 0; s < n_split; ++s) z += to_f32(in[(size_t)s * split_stride + (size_t)t * in_stride + c]);
+        out[(size_t)t * out_stride + c] = from_f32<TO>(activate(act, z, c0, c1));
+    }
+}
+
+extern "C" int odin_activation(const void* in, int in_dtype, int n_split, long long split_stride, long long in_stride,
+                               int act, const void* params, int params_dtype, void* out, int out_dtype,
+                               long long out_stride, int T, int n, void* stream) {
+    if (T <= 0 || n <= 0) return 0;
+    if (act < 0 || act > ACT_XIELU || (act == ACT_XIELU && params == nullptr)) return ODIN_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)T * n;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    VecRef pv{params, params_dtype == ODIN_BF16};
+#define GO(TI, TO)                                                                                              \
+    odin_launch(activation_kernel<TI, TO>, dim3(blocks), dim3(256), 0, s, (const TI*)in, n_split,               \
+                (size_t)split_stride, (size_t)in_stride, act, pv, (TO*)out, (size_t)out_stride, T, n)
+    if (in_dtype == ODIN_F32 && out_dtype == ODIN_F32) GO(float, float);
+    else if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16) GO(float, bf16);
+    else if (in_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(bf16, bf16);
+    else if (in_dtype == ODIN_BF16 && out_dtype == ODIN_F32) GO(bf16, float);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ gate x row of a per-token table
+// out[t, c] = act(sum_s gate[s][t, c]) * table[ids[t], col0 + c]
+template <typename TG, typename TT, typename TO>
+__global__ void __launch_bounds__(256)
+gated_lookup_kernel(const TG* __restrict__ gate, int n_split, size_t split_stride, int act, const TT* __restrict__ table,
+                    size_t table_stride, int col0, int V, const int* __restrict__ ids, TO* __restrict__ out, int T, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)T * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / n), c = (int)(i % n);
+        const int id = ids[t];
+        float z = 0.f;
+        for (int s = 0; s < n_split; ++s) z += to_f32(gate[(size_t)s * split_stride + (size_t)t * n + c]);
+        const float e = (id >= 0 && id < V) ? to_f32(table[(size_t)id * table_stride + col0 + c]) : 0.f;
+        out[(size_t)t * n + c] = from_f32<TO>(activate(act, z, 0.f, 0.f) * e);
+    }
+}
+
+extern "C" int odin_gated_lookup(const void* gate, int gate_dtype, int n_split, long long split_stride, int act,
+                                 const void* table, int table_dtype, long long table_stride, int col0, int V,
+                                 const int* ids, void* out, int out_dtype, int T, int n, void* stream) {
+    if (T <= 0 || n <= 0) return 0;
+    if (act < 0 || act > ACT_GELU_TANH) return ODIN_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)T * n;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+#define GO(TG, TT, TO)                                                                                          \
+    odin_launch(gated_lookup_kernel<TG, TT, TO>, dim3(blocks), dim3(256), 0, s, (const TG*)gate, n_split,       \
+                (size_t)split_stride, act, (const TT*)table, (size_t)table_stride, col0, V, ids, (TO*)out, T, n)
+    if (gate_dtype == ODIN_F32 && table_dtype == ODIN_F32 && out_dtype == ODIN_F32) GO(float, float, float);
+    else if (gate_dtype == ODIN_F32 && table_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(float, bf16, bf16);
+    else if (gate_dtype == ODIN_BF16 && table_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(bf16, bf16, bf16);
+    else if (gate_dtype == ODIN_F32 && table_dtype == ODIN_F32 && out_dtype == ODIN_BF16) GO(float, float, bf16);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}

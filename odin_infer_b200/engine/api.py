@@ -88,11 +88,10 @@ class Engine:
         itemsize = 4 if self.rt.dtype == torch.float32 else 2
         self.cache_bytes = 0
         for g in self.cache.groups.values():
-            shape = g.storage_shape()
-            k = torch.empty(shape, dtype=self.rt.dtype, device=self.rt.device)
-            v = torch.empty(shape, dtype=self.rt.dtype, device=self.rt.device)
+            k = torch.empty(g.storage_shape(), dtype=self.rt.dtype, device=self.rt.device)
+            v = torch.empty(g.value_storage_shape(), dtype=self.rt.dtype, device=self.rt.device)
             g.attach_storage(k, v)
-            self.cache_bytes += 2 * k.numel() * itemsize
+            self.cache_bytes += (k.numel() + v.numel()) * itemsize
         nstate = self.cache.state_bytes_per_slot
         self.cache.state = torch.zeros(self.cache.max_slots, nstate, dtype=torch.uint8, device=self.rt.device)
         self.cache.zero_state = (lambda slot: self.cache.state[slot].zero_()) if nstate else None

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import ParamSpec, build_part
+from ..parts.base import ParamSpec, build_part, split_update
 from ..parts.spec import ModelSpec
 
 
@@ -73,9 +73,16 @@ class DecoderModel:
     def register_cache(self, cache) -> None:
         """Tell the cache what every schedule entry keeps."""
         writes = []
-        for e in self.spec.schedule:
+        requests = [self.layers[e.layer].mixer.cache_request() for e in self.spec.schedule]
+        for idx, e in enumerate(self.spec.schedule):
             mixer = self.layers[e.layer].mixer
-            cache.add_entry(mixer.cache_request(), mixer.state_bytes(), e.reads_cache_of)
+            kv = requests[idx]
+            if kv is not None and e.reads_cache_of is None:
+                # a line keeps what its writer and every entry that reads it can see
+                readers = [requests[j] for j, o in enumerate(self.spec.schedule)
+                           if o.reads_cache_of == idx and requests[j] is not None]
+                kv = type(kv).keeping_for_all([kv] + readers)
+            cache.add_entry(kv, mixer.state_bytes(), e.reads_cache_of)
             writes.append(e.reads_cache_of is None)
         cache.entry_writes = writes
 
@@ -89,5 +96,9 @@ class DecoderModel:
             x, pending = self.layers[e.layer].forward(rt, step, x, pending, idx)
         if step.n_logit_rows == 0:
             return None
-        h = self.final_norm.forward(rt, x, pending, rows=step.logit_rows)
+        delta, bias = split_update(pending)
+        if bias is None:
+            h = self.final_norm.forward(rt, x, delta, rows=step.logit_rows)
+        else:
+            h = self.final_norm.forward(rt, x, delta, rows=step.logit_rows, bias=bias)
         return self.head.forward(rt, step, h)

@@ -232,10 +232,27 @@ class Runtime:
                                           k_line, v_line, step.tok_pos, step.tok_seq, block_table, window, scratch,
                                           n_split, write_kv)
 
-    def attention(self, step, q, out, n_q, n_kv, head_dim, k_line, v_line, block_table, window) -> None:
+    def settle(self, x: torch.Tensor, delta, bias) -> torch.Tensor:
+        """Adds an update that was still pending (and its bias) to the residual stream x, and returns x in
+        the element type of activations (x itself in the 32-bit engine) for a product that reads it."""
+        if self.dtype == torch.float32:
+            if delta is not None or bias is not None:
+                ops.row_update(x, delta, bias, None, 0.0, 1, None, normalise=False)
+            return x
+        out = self.empty(x.shape[0], x.shape[1])
+        ops.row_update(x, delta, bias, None, 0.0, 1, out, normalise=False)
+        return out
+
+    def attention(self, step, q, out, n_q, n_kv, head_dim, k_line, v_line, block_table, window, chunk: int = 0,
+                  scale: float = 0.0, softcap: float = 0.0, v_head_dim: int | None = None) -> None:
         """bfloat16: one token per sequence goes to the split-key kernel, prompts (and pieces
         of prompts) to the flash kernel.  The 32-bit path and head sizes that the fast
-        kernels refuse go to the plain kernel."""
+        kernels refuse go to the plain kernel, and so does whatever those kernels do not know:
+        a chunk mask, a scale of its own, a cap on the scores, value heads of another size."""
+        if chunk or scale or softcap or (v_head_dim or head_dim) != head_dim:
+            ops.attention_plain(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
+                                window, chunk, scale, softcap, v_head_dim)
+            return
         if self.dtype == torch.bfloat16 and step.all_single and ops.attention_decode_supported(head_dim):
             B = q.shape[0]
             n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms)

@@ -199,7 +199,7 @@ class StepBatch:
         self.max_len_after += 1
         self.all_start = False
         for key, g in self.cache.groups.items():
-            if g.request.window > 0 or any(p % PAGE == 0 for p in start_positions):
+            if g.request.window > 0 or g.request.chunk > 0 or any(p % PAGE == 0 for p in start_positions):
                 self._h(("bt", key))[:n] = g.block_table[self.slots]
         self._last_starts = list(start_positions)
         self._upload()

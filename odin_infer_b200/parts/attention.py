@@ -5,7 +5,7 @@ import torch
 
 from ..cache import KVRequest
 from ..csrc import ops
-from .base import Mixer, ParamSpec, register_part
+from .base import Biased, Mixer, ParamSpec, register_part
 
 
 @register_part("mixer", "gqa_attention")
@@ -14,23 +14,40 @@ class GQAttention(Mixer):
     causal attention of each query head h over kv head h // (n_q / n_kv), output
     projection.  Restates infer/forward.odin:53-117.
 
-    window > 0 keeps only the last `window` keys visible.  kv_shared: this mixer has
+    window > 0 keeps only the last `window` keys visible; chunk > 0 only the keys of the query's own
+    chunk of `chunk` positions (counted from the sequence's first position).  kv_shared: this mixer has
     no k and v of its own and reads the cache line its schedule entry names.
     The three projection matrices are fused into one at load time.
+
+    qk_norm: True: RMSNorm with the weights `q_norm` / `k_norm` before the rotation; "unit_after":
+    q and k heads divided by their root mean square after the rotation, no weight; False: none.
+    biases: names of bias vectors of the projections ({"q", "k", "v", "o"}), added in the projection.
+    scale: factor on q . k (0: 1 / sqrt(head_dim)).  softcap > 0: scores become
+    softcap * tanh(score / softcap) before the softmax.  v_head_dim: size of a value head (0: head_dim).
     """
 
     graph_safe = True
 
     def __init__(self, width: int, n_q_heads: int, n_kv_heads: int, head_dim: int, names: dict,
-                 position_encoding: str | None = None, qk_norm: bool = True, eps: float = 1e-6,
-                 window: int = 0, kv_shared: bool = False):
+                 position_encoding: str | None = None, qk_norm=True, eps: float = 1e-6,
+                 window: int = 0, kv_shared: bool = False, chunk: int = 0, biases: dict | None = None,
+                 scale: float = 0.0, softcap: float = 0.0, v_head_dim: int = 0):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads are not a multiple of {n_kv_heads} kv heads")
+        if qk_norm not in (True, False, "unit_after"):
+            raise ValueError(f"qk_norm must be True, False or 'unit_after', got {qk_norm!r}")
         self.width, self.n_q, self.n_kv, self.hd = width, n_q_heads, n_kv_heads, head_dim
+        self.vd = int(v_head_dim) or head_dim
         self.names, self.pe_name = dict(names), position_encoding
-        self.qk_norm, self.eps, self.window, self.kv_shared = qk_norm, float(eps), int(window), kv_shared
+        self.qk_norm, self.eps, self.window, self.kv_shared = qk_norm is True, float(eps), int(window), kv_shared
+        self.unit_after = qk_norm == "unit_after"
+        self.chunk, self.scale, self.softcap = int(chunk), float(scale), float(softcap)
+        self.bias_names = dict(biases) if biases else None
+        # the heads as the first architecture has them: the fast kernels' ground
+        self.plain_heads = (self.bias_names is None and not self.unit_after and self.vd == self.hd
+                            and self.chunk == 0 and self.scale == 0.0 and self.softcap == 0.0)
         self.pe = None          # set by the model from pe_name
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.b_qkv = self.b_o = None
         self._dummy = None
 
     def params(self):
@@ -38,12 +55,18 @@ class GQAttention(Mixer):
         out = [ParamSpec(n["q"], (self.n_q * self.hd, self.width))]
         if not self.kv_shared:
             out += [ParamSpec(n["k"], (self.n_kv * self.hd, self.width)),
-                    ParamSpec(n["v"], (self.n_kv * self.hd, self.width))]
-        out.append(ParamSpec(n["o"], (self.width, self.n_q * self.hd)))
+                    ParamSpec(n["v"], (self.n_kv * self.vd, self.width))]
+        out.append(ParamSpec(n["o"], (self.width, self.n_q * self.vd)))
         if self.qk_norm:
             out.append(ParamSpec(n["q_norm"], (self.hd,), init="norm"))
             if not self.kv_shared:
                 out.append(ParamSpec(n["k_norm"], (self.hd,), init="norm"))
+        if self.bias_names is not None:
+            b = self.bias_names
+            out.append(ParamSpec(b["q"], (self.n_q * self.hd,)))
+            if not self.kv_shared:
+                out += [ParamSpec(b["k"], (self.n_kv * self.hd,)), ParamSpec(b["v"], (self.n_kv * self.vd,))]
+            out.append(ParamSpec(b["o"], (self.width,)))
         return out
 
     def bind(self, tensors, rt):
@@ -61,10 +84,17 @@ class GQAttention(Mixer):
             self.k_norm = tensors[n["k_norm"]] if not self.kv_shared else self.q_norm
             if self.q_norm.dtype != self.k_norm.dtype:
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+        if self.bias_names is not None:
+            b = self.bias_names
+            parts = [tensors[b["q"]]] if self.kv_shared else [tensors.pop(b["q"]), tensors.pop(b["k"]), tensors.pop(b["v"])]
+            if len({t.dtype for t in parts}) > 1:
+                parts = [t.float() for t in parts]
+            self.b_qkv = torch.cat(parts, dim=0).contiguous()
+            self.b_o = tensors[b["o"]]
         self._dummy = torch.zeros(1, 1, dtype=torch.float32, device=rt.device)
 
     def cache_request(self):
-        return KVRequest(self.n_kv, self.hd, self.window)
+        return KVRequest(self.n_kv, self.hd, self.window, self.chunk, self.vd if self.vd != self.hd else 0)
 
     def kernel_groups(self):
         return {"head_prep", "attention_plain", "gemm_plain"}
@@ -102,7 +132,18 @@ class GQAttention(Mixer):
         rot = self.pe.rotation() if self.pe is not None else None
         cos, sin, rot_dim = rot if rot is not None else (self._dummy, self._dummy, 0)
         writes = step.writes_cache(entry) and not self.kv_shared
-        o = rt.empty(T, self.n_q * self.hd)
+        o = rt.empty(T, self.n_q * self.vd)
+        if not self.plain_heads:
+            q_out = rt.empty(T, self.n_q * self.hd)
+            q = ops.head_prep(qkv, self.n_q, 0 if self.kv_shared else self.n_kv, self.hd,
+                              self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps,
+                              cos, sin, rot_dim, step.tok_pos, step.tok_seq, block_table, k_line, v_line,
+                              write_kv=writes, q_out=q_out, bias=self.b_qkv, unit_norm_after=self.unit_after,
+                              v_head_dim=self.vd)
+            rt.attention(step, q, o, self.n_q, self.n_kv, self.hd, k_line, v_line, block_table, self.window,
+                         chunk=self.chunk, scale=self.scale, softcap=self.softcap, v_head_dim=self.vd)
+            out = rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True, add_to=residual)
+            return out if self.b_o is None else Biased(out, self.b_o)
         # decoding: the attention kernel may prepare its heads itself
         if not self.kv_shared and rt.attention_with_head_prep(
                 step, qkv, o, self.n_q, self.n_kv, self.hd, self.q_norm if self.qk_norm else None,

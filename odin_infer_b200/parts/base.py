@@ -36,13 +36,29 @@ class ParamSpec:
     """One tensor of the model folder.
 
     init: how random-weights mode fills it: "matrix" N(0, 0.02), "norm" 1 + N(0, 0.1),
-    "zeros", or "int_table" (int32 zeros).  alias_of: the name of another tensor that
-    stands in when this one is absent (a tied head).
+    "unit" 0.5 + N(0, 0.15) (mixing weights and lower bounds between 0 and 1), "decay"
+    -2 + N(0, 1) (what a double exponential turns into a decay), "zeros", or "int_table"
+    (int32 zeros).  alias_of: the name of another tensor that stands in when this one is
+    absent (a tied head).  A dimension of -1 in `shape` takes whatever the model folder
+    holds (a size that no configuration key gives); `shape_if_random` is then the shape
+    that random-weights mode writes.
     """
     name: str
     shape: tuple[int, ...]
     init: str = "matrix"
     alias_of: str | None = None
+    shape_if_random: tuple[int, ...] | None = None
+
+    def matches(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w in (-1, h) for w, h in zip(self.shape, shape))
+
+    @property
+    def concrete_shape(self) -> tuple[int, ...]:
+        shape = self.shape_if_random if (self.shape_if_random is not None and -1 in self.shape) else self.shape
+        if -1 in shape:
+            raise ValueError(f"tensor '{self.name}': a dimension of its shape {self.shape} is known from a model folder only")
+        return tuple(shape)
 
     @property
     def is_integer(self) -> bool:
@@ -83,12 +99,35 @@ class ResidualAdded:
     into "no pending update" before the next norm sees it."""
 
 
+class Biased:
+    """An update of the residual stream that still lacks a bias: `update` (a tensor, or
+    `ResidualAdded()` when the product has added itself already) plus `bias` [width] on every row.
+    Whoever adds the update (the next norm, a block's extra) adds the bias with it."""
+
+    def __init__(self, update, bias: torch.Tensor):
+        self.update, self.bias = update, bias
+
+
+def split_update(pending):
+    """(delta, bias) of what a mixer or feed-forward answered: each a tensor or None."""
+    bias = None
+    if isinstance(pending, Biased):
+        pending, bias = pending.update, pending.bias
+    if isinstance(pending, ResidualAdded):
+        pending = None
+    return pending, bias
+
+
 class Norm(Part):
     def forward(self, rt, x: torch.Tensor, delta, rows: torch.Tensor | None = None):
         """x: the 32-bit residual stream [n, width], updated in place by `delta`
         (None, [n, width] or [splits, n, width]); returns the normalised rows in
-        the runtime's element type.  rows: gather these rows only (x untouched)."""
+        the runtime's element type.  rows: gather these rows only (x untouched).
+        A norm that sets `takes_bias` also takes a keyword `bias=` ([width], added to every
+        row with the update); only such a norm may follow a part that answers `Biased`."""
         raise NotImplementedError
+
+    takes_bias = False
 
 
 class PositionEncoding(Part):
@@ -143,6 +182,16 @@ class Block(Part):
         raise NotImplementedError
 
 
+class BlockExtra(Part):
+    """What a block does to the residual stream after its mixer and feed-forward (an input of its
+    own from the tokens, for instance)."""
+
+    def forward(self, rt, step, x: torch.Tensor, pending):
+        """x: the residual stream; pending: the update not yet added (as a mixer answers it).
+        Returns (x, pending)."""
+        raise NotImplementedError
+
+
 class Embedding(Part):
     def forward(self, rt, step) -> torch.Tensor:
         raise NotImplementedError
@@ -156,7 +205,8 @@ class Head(Part):
 
 # ---------------------------------------------------------------- registries
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {}, "embedding": {}, "head": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {}, "block_extra": {},
+    "embedding": {}, "head": {},
 }
 
 

@@ -1,28 +1,34 @@
 """How a layer's parts are arranged."""
 from __future__ import annotations
 
-from .base import Block, PartSpec, ResidualAdded, build_part, register_part
+from .base import Block, PartSpec, build_part, register_part, split_update
 
 
 @register_part("block", "prenorm")
 class PreNormBlock(Block):
-    """x -> x + Mixer(Norm(x)) -> x + FeedForward(Norm(x)) (infer/forward.odin:51, :117-139).
+    """x -> x + Mixer(Norm(x)) -> x + FeedForward(Norm(x)) (infer/forward.odin:51, :117-139), then the
+    block's extras in order (each sees the residual stream with everything before it added).
 
     Each residual add is carried out by the norm that follows it: the block hands
-    the update it has not yet added to whoever runs next."""
+    the update it has not yet added to whoever runs next.  A block may have no feed-forward
+    (and then no second norm)."""
 
-    def __init__(self, mixer: PartSpec, feed_forward: PartSpec, norm_mixer: PartSpec, norm_feed_forward: PartSpec):
+    def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, norm_mixer: PartSpec,
+                 norm_feed_forward: PartSpec | None, extras: tuple = ()):
+        if (feed_forward is None) != (norm_feed_forward is None):
+            raise ValueError("a block has a feed-forward and its norm, or neither")
         self._mixer = build_part("mixer", mixer)
-        self.ffn = build_part("feed_forward", feed_forward)
+        self.ffn = build_part("feed_forward", feed_forward) if feed_forward is not None else None
         self.norm_mixer = build_part("norm", norm_mixer)
-        self.norm_ffn = build_part("norm", norm_feed_forward)
+        self.norm_ffn = build_part("norm", norm_feed_forward) if norm_feed_forward is not None else None
+        self.extras = [build_part("block_extra", e) for e in extras]
 
     @property
     def mixer(self):
         return self._mixer
 
     def _parts(self):
-        return (self.norm_mixer, self._mixer, self.norm_ffn, self.ffn)
+        return tuple(p for p in (self.norm_mixer, self._mixer, self.norm_ffn, self.ffn, *self.extras) if p is not None)
 
     def params(self):
         return [p for part in self._parts() for p in part.params()]
@@ -41,10 +47,23 @@ class PreNormBlock(Block):
     def graph_safe(self):
         return all(p.graph_safe for p in self._parts())
 
+    @staticmethod
+    def _norm(norm, rt, x, pending):
+        delta, bias = split_update(pending)
+        if bias is None:
+            return norm.forward(rt, x, delta)
+        if not norm.takes_bias:
+            raise TypeError(f"{type(norm).__name__} follows a part whose update carries a bias, and takes none")
+        return norm.forward(rt, x, delta, bias=bias)
+
     def forward(self, rt, step, x, pending, entry):
         mixer, ffn = self._mixer, self.ffn
-        h = self.norm_mixer.forward(rt, x, pending)
-        delta = mixer.forward(rt, step, h, entry, residual=x) if mixer.takes_residual else mixer.forward(rt, step, h, entry)
-        h = self.norm_ffn.forward(rt, x, None if isinstance(delta, ResidualAdded) else delta)
-        delta = ffn.forward(rt, step, h, residual=x) if ffn.takes_residual else ffn.forward(rt, step, h)
-        return x, (None if isinstance(delta, ResidualAdded) else delta)
+        h = self._norm(self.norm_mixer, rt, x, pending)
+        pending = mixer.forward(rt, step, h, entry, residual=x) if mixer.takes_residual else mixer.forward(rt, step, h, entry)
+        if ffn is not None:
+            h = self._norm(self.norm_ffn, rt, x, pending)
+            pending = ffn.forward(rt, step, h, residual=x) if ffn.takes_residual else ffn.forward(rt, step, h)
+        for extra in self.extras:
+            x, pending = extra.forward(rt, step, x, pending)
+        delta, bias = split_update(pending)
+        return x, (pending if bias is not None else delta)

@@ -4,31 +4,37 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Embedding, Head, ParamSpec, register_part
+from .base import Embedding, Head, ParamSpec, PartSpec, build_part, register_part
 
 
 @register_part("embedding", "token_table")
 class TokenEmbedding(Embedding):
-    """x = E[token], no scaling (infer/forward.odin:43)."""
+    """x = E[token], no scaling (infer/forward.odin:43).  norm: a norm (a PartSpec of a norm that can
+    work in place) through which the embedded rows pass before they become the residual stream."""
 
     graph_safe = True
 
-    def __init__(self, vocab_size: int, width: int, weight: str):
+    def __init__(self, vocab_size: int, width: int, weight: str, norm: PartSpec | None = None):
         self.vocab_size, self.width, self.weight_name = vocab_size, width, weight
+        self.norm = build_part("norm", norm) if norm is not None else None
         self.table = None
 
     def params(self):
-        return [ParamSpec(self.weight_name, (self.vocab_size, self.width))]
+        return [ParamSpec(self.weight_name, (self.vocab_size, self.width))] + (self.norm.params() if self.norm else [])
 
     def bind(self, tensors, rt):
         self.table = tensors[self.weight_name]
+        if self.norm is not None:
+            self.norm.bind(tensors, rt)
 
     def kernel_groups(self):
-        return {"elementwise"}
+        return {"elementwise"} | (self.norm.kernel_groups() if self.norm else set())
 
     def forward(self, rt, step):
         x = rt.empty(step.n_rows, self.width, dtype=torch.float32)
         ops.embed(self.table, step.tok_ids, x)
+        if self.norm is not None:
+            self.norm.in_place(rt, x)
         return x
 
 

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import torch
 
+from ..csrc import ops
 from .base import FeedForward, ParamSpec, register_part
 
 
@@ -44,4 +45,42 @@ class SwiGLU(FeedForward):
 
     def forward(self, rt, step, h, residual=None):
         act = rt.gated_linear(h, self.w_gate_up, self.inner)
+        return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True, add_to=residual)
+
+
+@register_part("feed_forward", "activated")
+class ActivatedMLP(FeedForward):
+    """down( act( up(x) ) ), no gate and no bias.  activation: one of `ops.ACTIVATIONS`; "xielu" reads its
+    two numbers (p, q) from the tensor `names["act"]`:
+    z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z/2."""
+
+    graph_safe = True
+    takes_residual = True
+
+    def __init__(self, width: int, inner: int, names: dict, activation: str = "xielu"):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation '{activation}' (known: {', '.join(ops.ACTIVATIONS)})")
+        self.width, self.inner, self.names, self.activation = width, inner, dict(names), activation
+        self.w_up = self.w_down = self.act_params = None
+
+    def params(self):
+        n = self.names
+        out = [ParamSpec(n["up"], (self.inner, self.width)), ParamSpec(n["down"], (self.width, self.inner))]
+        if self.activation == "xielu":
+            out.append(ParamSpec(n["act"], (2,), init="unit"))
+        return out
+
+    def bind(self, tensors, rt):
+        n = self.names
+        self.w_up, self.w_down = tensors[n["up"]], tensors[n["down"]]
+        if self.activation == "xielu":
+            self.act_params = tensors[n["act"]]
+
+    def kernel_groups(self):
+        return {"rowwise", "gemm_plain"}
+
+    def forward(self, rt, step, h, residual=None):
+        up = rt.linear(h, self.w_up, may_split=True)
+        act = rt.empty(h.shape[0], self.inner)
+        ops.activation(up, self.activation, act, self.act_params)
         return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True, add_to=residual)

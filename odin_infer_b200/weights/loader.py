@@ -42,7 +42,7 @@ def check_folder(files: ModelFiles, specs: list[ParamSpec]) -> dict[str, str]:
             continue
         source[s.name] = src
         shape, dt = files.shape(src), files.dtype(src)
-        if tuple(shape) != tuple(s.shape):
+        if not s.matches(shape):
             wrong.append(f"{src}: shape {list(shape)}, expected {list(s.shape)}")
         elif s.is_integer and dt not in _INTS:
             wrong.append(f"{src}: element type {dt}, expected an integer type")

@@ -36,7 +36,7 @@ from .safetensors_io import write_safetensors
 _M64 = (1 << 64) - 1
 _SIGMA_S = math.sqrt(8.0 * (65536.0 ** 2 - 1.0) / 12.0)
 _CENTER = 4 * 65535
-_INIT = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1)}   # mean, standard deviation
+_INIT = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1), "unit": (0.5, 0.15), "decay": (-2.0, 1.0)}   # mean, standard deviation
 
 
 def _mix64(z: int) -> int:
@@ -108,18 +108,19 @@ def host_tensor(name: str, shape, init: str, seed: int, dtype: torch.dtype, firs
 
 def random_tensor(spec: ParamSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
     """The tensor of `spec` under `seed`, stored as `dtype`; the same bits on the host and on a CUDA device."""
+    shape = spec.concrete_shape
     if spec.is_integer:
-        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        return torch.zeros(shape, dtype=torch.int32, device=device)
     if spec.init == "zeros":
-        return torch.zeros(spec.shape, dtype=dtype, device=device)
+        return torch.zeros(shape, dtype=dtype, device=device)
     if spec.init not in _INIT:
         raise ValueError(f"tensor '{spec.name}': unknown init '{spec.init}'")
     if torch.device(device).type != "cuda":
-        return host_tensor(spec.name, spec.shape, spec.init, seed, dtype)
+        return host_tensor(spec.name, shape, spec.init, seed, dtype)
     from ..csrc import ops
     mean, std = _INIT[spec.init]
     store = dtype if dtype in (torch.bfloat16, torch.float32) else torch.float32
-    t = torch.empty(spec.shape, dtype=store, device=device)
+    t = torch.empty(shape, dtype=store, device=device)
     ops.random_fill(t, stream_key(seed, spec.name), mean, float(np.float32(std / _SIGMA_S)))
     return t.to(dtype)
 
@@ -144,7 +145,7 @@ def write_random_model(folder: str, config: ModelConfig, seed: int, dtype: torch
     by_name = {p.name: p for p in params}
     write_safetensors(
         os.path.join(folder, "model.safetensors"),
-        [(p.name, torch.int32 if p.is_integer else dtype, tuple(p.shape)) for p in params],
+        [(p.name, torch.int32 if p.is_integer else dtype, p.concrete_shape) for p in params],
         lambda name: random_tensor(by_name[name], seed, dtype),
         metadata={"format": "pt", "seed": seed})
     return folder
