@@ -80,9 +80,11 @@ def main(argv=None) -> int:
     if args.prompt_file:
         with open(args.prompt_file) as f:
             prompts += [parse_ids(line) for line in f if line.strip()]
-    vocab = (config or load_config(args.model)).to_dict().get("vocab_size", 0)
     if args.random_prompts:
         import numpy as np
+        from .config import lookup_architecture
+        cfg = config or load_config(args.model)
+        vocab = lookup_architecture(cfg.architecture).build_spec(cfg).vocab_size
         n, length = (int(v) for v in args.random_prompts.split(":"))
         rng = np.random.default_rng(1)
         prompts += [rng.integers(0, vocab, length).tolist() for _ in range(n)]

@@ -73,6 +73,8 @@ def build_tovalix_spec(cfg: TovalixConfig) -> ModelSpec:
         schedule=tuple(schedule),
         final_norm=norm("final.norm"),
         head=PartSpec("linear", dict(vocab_size=cfg.vocab, width=cfg.width, weight="head")),
+        # a layer without a feed-forward has no use for a second norm; a folder that stores one is still read
+        tolerated_tensors=tuple(f"l{i}.norm2" for i, l in enumerate(cfg.layers) if not l.ff),
     )
 
 

@@ -54,7 +54,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32)
 attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv, const bf16* __restrict__ k_cache,
                    const bf16* __restrict__ v_cache, int page_size, const int* __restrict__ tok_pos,
                    const int* __restrict__ tok_seq, const int* __restrict__ block_table, int bt_stride, int window,
-                   float scale_log2, float* __restrict__ part_acc, float* __restrict__ part_ml, int n_split) {
+                   int chunk, float scale_log2, float cap_log2, float* __restrict__ part_acc,
+                   float* __restrict__ part_ml, int n_split) {
     using GE = Geo<HD>;
     constexpr int EPL = GE::EPL, LPK = GE::LPK, KPI = GE::KPI;
     pdl_trigger();
@@ -79,6 +80,7 @@ attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv,
         const int pos = tok_pos[t];
         int first = 0;
         if (window > 0 && pos - window + 1 > 0) first = pos - window + 1;
+        if (chunk > 0) first = max(first, (pos / chunk) * chunk);
         const int p_first = first / page_size, p_last = pos / page_size;
         const int n_pages = p_last - p_first + 1;
         const int per = (n_pages + n_split - 1) / n_split;
@@ -126,6 +128,7 @@ attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv,
             for (int e = 0; e < EPL; ++e) s = fmaf(qf[h][e], kf[e], s);
 #pragma unroll
             for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (cap_log2 > 0.f) s = cap_log2 * tanhf(s / cap_log2);
             if (have) {
                 const float m_new = fmaxf(m[h], s);
                 const float corr = exp2f(m[h] - m_new);
@@ -261,19 +264,31 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const fl
     }
 }
 
+// What a caller may set beside the window: a chunk mask, a factor on q . k other than 1 / sqrt(hd),
+// a cap on the scores (softcap * tanh(score / softcap)).  All zero: none of them.
+struct ScoreOpts {
+    int chunk = 0;
+    float scale = 0.f;
+    float softcap = 0.f;
+    float scale_log2(int hd) const { return 1.4426950408889634f * (scale > 0.f ? scale : 1.0f / sqrtf((float)hd)); }
+    float cap_log2() const { return softcap > 0.f ? 1.4426950408889634f * softcap : 0.f; }
+};
+
 template <int HD>
 int launch_decode(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, int B, int Hq, int Hkv,
                   const bf16* k_cache, const bf16* v_cache, int page_size, const int* tok_pos, const int* tok_seq,
                   const int* block_table, int bt_stride, int window, float* part_acc, float* part_ml, int n_split,
-                  cudaStream_t s) {
+                  cudaStream_t s, const ScoreOpts& so = ScoreOpts()) {
     const int g = Hq / Hkv;
-    const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+    const float scale_log2 = so.scale_log2(HD);
+    const int chunk = so.chunk;
+    const float cap_log2 = so.cap_log2();
 #define GO(G)                                                                                                      \
     do {                                                                                                           \
         dim3 grid(n_split, Hkv * ((g + G - 1) / G), B);                                                            \
         odin_launch(attn_decode_kernel<HD, G>, grid, dim3(AD_WARPS * 32), 0, s, q, q_stride, Hq, Hkv, k_cache,      \
-                    v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride, window, scale_log2, part_acc,    \
-                    part_ml, n_split);                                                                             \
+                    v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride, window, chunk, scale_log2,       \
+                    cap_log2, part_acc, part_ml, n_split);                                                                           \
     } while (0)
     if (g == 1) GO(1);
     else if (g == 2) GO(2);
@@ -347,7 +362,7 @@ template <int HD>
 int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, int B, int Hq, int Hkv,
                      const bf16* k_cache, const bf16* v_cache, int n_pages, const int* tok_pos, const int* tok_seq,
                      const int* block_table, int bt_stride, int window, float* part_acc, float* part_ml, int n_split,
-                     cudaStream_t s, const PrepArgs* prep = nullptr) {
+                     cudaStream_t s, const PrepArgs* prep = nullptr, const ScoreOpts& so = ScoreOpts()) {
     // the result is written with 8-byte stores
     if ((out_stride % 4) != 0 || (((uintptr_t)out) & 7) != 0) return ODIN_ERR_UNSUPPORTED;
     CUtensorMap mk, mv;
@@ -360,7 +375,9 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
     p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
     p.Hq = Hq; p.Hkv = Hkv; p.tok_pos = tok_pos; p.tok_seq = tok_seq;
     p.block_table = block_table; p.bt_stride = bt_stride; p.window = window;
-    p.scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+    p.scale_log2 = so.scale_log2(HD);
+    p.chunk = so.chunk;
+    p.cap_log2 = so.cap_log2();
     p.part_acc = part_acc; p.part_ml = part_ml; p.n_split = n_split;
     p.error = decode_error_flag();
     p.counters = split_counters();
@@ -424,11 +441,17 @@ extern "C" int odin_attention_decode_supported(int hd) {
 // belongs to sequence tok_seq[t] (row of the block table; negative: padding, skipped)
 // at position tok_pos[t].  n_pages: pages of the cache line (0: unknown, the tensor-core
 // kernel is then not used).  scratch: odin_attention_decode_scratch(...) floats.
-extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void* out, long long out_row_stride, int B,
-                                     int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache, int page_size,
-                                     int n_pages, const int* tok_pos, const int* tok_seq, const int* block_table,
-                                     int bt_stride, int window, float* scratch, int n_split, void* stream) {
+// odin_attention_decode_masked: the same with a chunk mask (chunk > 0: only the keys of the query's own chunk of
+// that many positions), a factor on q . k of the caller's (scale > 0) and capped scores (softcap > 0).
+extern "C" int odin_attention_decode_masked(const void* q, long long q_row_stride, void* out, long long out_row_stride,
+                                            int B, int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache,
+                                            int page_size, int n_pages, const int* tok_pos, const int* tok_seq,
+                                            const int* block_table, int bt_stride, int window, int chunk, float scale,
+                                            float softcap, float* scratch, int n_split, void* stream) {
     if (B <= 0) return 0;
+    if (chunk < 0 || scale < 0.f || softcap < 0.f) return ODIN_ERR_BAD_ARG;
+    ScoreOpts so;
+    so.chunk = chunk; so.scale = scale; so.softcap = softcap;
     if (Hkv <= 0 || Hq % Hkv != 0 || n_split < 1 || scratch == nullptr) return ODIN_ERR_BAD_ARG;
     if (B > 65535 || Hq > 65535 || n_split > 65535) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -441,15 +464,15 @@ extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void
         if (hd == 64)
             return launch_decode_tc<64>((const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, B, Hq,
                                         Hkv, (const bf16*)k_cache, (const bf16*)v_cache, n_pages, tok_pos, tok_seq,
-                                        block_table, bt_stride, window, part_acc, part_ml, n_split, s);
+                                        block_table, bt_stride, window, part_acc, part_ml, n_split, s, nullptr, so);
         return launch_decode_tc<128>((const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, B, Hq,
                                      Hkv, (const bf16*)k_cache, (const bf16*)v_cache, n_pages, tok_pos, tok_seq,
-                                     block_table, bt_stride, window, part_acc, part_ml, n_split, s);
+                                     block_table, bt_stride, window, part_acc, part_ml, n_split, s, nullptr, so);
     }
 #define CALL(HD)                                                                                                  \
     return launch_decode<HD>((const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, B, Hq, Hkv, \
                              (const bf16*)k_cache, (const bf16*)v_cache, page_size, tok_pos, tok_seq, block_table, \
-                             bt_stride, window, part_acc, part_ml, n_split, s)
+                             bt_stride, window, part_acc, part_ml, n_split, s, so)
     switch (hd) {
         case 16: CALL(16);
         case 32: CALL(32);
@@ -459,6 +482,15 @@ extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void
         default: return ODIN_ERR_UNSUPPORTED;
     }
 #undef CALL
+}
+
+extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void* out, long long out_row_stride, int B,
+                                     int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache, int page_size,
+                                     int n_pages, const int* tok_pos, const int* tok_seq, const int* block_table,
+                                     int bt_stride, int window, float* scratch, int n_split, void* stream) {
+    return odin_attention_decode_masked(q, q_row_stride, out, out_row_stride, B, Hq, Hkv, hd, k_cache, v_cache, page_size,
+                                        n_pages, tok_pos, tok_seq, block_table, bt_stride, window, 0, 0.f, 0.f, scratch,
+                                        n_split, stream);
 }
 
 // Decode attention that prepares its own heads: qkv is the fused projection's output for the

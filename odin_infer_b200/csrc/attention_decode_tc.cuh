@@ -25,7 +25,9 @@ struct DecodeTcParams {
     const int* block_table;
     int bt_stride;
     int window;
+    int chunk;        // > 0: only the keys of the query's own chunk of this many positions
     float scale_log2;
+    float cap_log2;   // > 0: scores (in log2 units) become cap_log2 * tanh(score / cap_log2)
     float* part_acc;
     float* part_ml;
     int n_split;
@@ -125,7 +127,7 @@ template <int HD>
 __device__ __forceinline__ void attend_page(const uint32_t sK_u, const uint32_t sV_u, const uint32_t (&qa)[HD / 16][4],
                                             float (&o)[HD / 8][4], float (&m_run)[2], float (&l_run)[2],
                                             const int page_key0, const int t_lo, const int t_hi, const float scale_log2,
-                                            const int lane) {
+                                            const float cap_log2, const int lane) {
     using namespace attn;
     constexpr int KB = HD / 16, NB_O = HD / 8;
     // S = Q K^T for the page's 64 keys: eight blocks of eight keys
@@ -152,6 +154,7 @@ __device__ __forceinline__ void attend_page(const uint32_t sK_u, const uint32_t 
         for (int j = 0; j < 4; ++j) {
             const int tk = key0 + nb * 8 + (j & 1);
             float v = s[nb][j] * scale_log2;
+            if (cap_log2 > 0.f) v = cap_log2 * tanhf(v / cap_log2);
             if (tk < t_lo || tk >= t_hi) v = -CUDART_INF_F;
             s[nb][j] = v;
             mx[j >> 1] = fmaxf(mx[j >> 1], v);
@@ -239,6 +242,7 @@ __device__ __forceinline__ void attn_decode_tc_body(const CUtensorMap& map_k, co
     const int pos = p.tok_pos[t];
     int first = 0;
     if (p.window > 0 && pos - p.window + 1 > 0) first = pos - p.window + 1;
+    if (p.chunk > 0) first = max(first, (pos / p.chunk) * p.chunk);
     const int p_first = first / PAGE_T, p_last = pos / PAGE_T;
     const int per = (p_last - p_first + 1 + p.n_split - 1) / p.n_split;
     const int pa = p_first + split * per, pb = min(p_last + 1, pa + per);  // pages [pa, pb)
@@ -389,7 +393,7 @@ __device__ __forceinline__ void attn_decode_tc_body(const CUtensorMap& map_k, co
                 __syncwarp();
             }
         }
-        attend_page<HD>(sK_u, sV_u, qa, o, m_run, l_run, pg * PAGE_T, t_lo, t_hi, p.scale_log2, lane);
+        attend_page<HD>(sK_u, sV_u, qa, o, m_run, l_run, pg * PAGE_T, t_lo, t_hi, p.scale_log2, p.cap_log2, lane);
         __syncwarp();  // every lane is done with the slot
         if (lane == 0 && i + SLOTS < n_here) issue(i + SLOTS, slot);
     }

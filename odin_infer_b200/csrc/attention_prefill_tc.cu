@@ -64,7 +64,9 @@ struct PrefillTcParams {
     const int* block_table;
     int bt_stride;
     int window;
+    int chunk;        // > 0: a query sees only the keys of its own chunk of this many positions
     float scale_log2;
+    float cap_log2;   // > 0: scores (in log2 units) become cap_log2 * tanh(score / cap_log2)
     int* error;
     int n_heads, n_seqs, n_tile_levels;  // the work: (head, sequence, tile) triples, heaviest tile level first
 };
@@ -189,6 +191,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     int first_key = 0;
     if (p.window > 0 && pos0 - p.window + 1 > 0) first_key = pos0 - p.window + 1;
+    if (p.chunk > 0) first_key = max(first_key, (pos0 / p.chunk) * p.chunk);  // the tile's first row sees furthest back
     const int page_a = first_key / PAGE_T, page_b = (pos0 + rows - 1) / PAGE_T;  // inclusive
     const int n_pages = page_b - page_a + 1;
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
@@ -316,7 +319,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const int row = quarter * 32 + lane;
         const int pos = pos0 + row;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const float scale = p.scale_log2;
+        // capped scores are brought to log2 units as they are capped; nothing is left to scale then
+        const float scale = p.cap_log2 > 0.f ? 1.0f : p.scale_log2;
+        const float cap = p.cap_log2, cap_in = p.cap_log2 > 0.f ? 2.0f * 1.4426950408889634f * p.scale_log2 / p.cap_log2 : 0.f;
+        const int chunk_lo = p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0;
         float m_run = -CUDART_INF_F;   // the maximum that the sums and O are scaled by (in log2 units)
         float l_run = 0.f;             // this thread's share of the row's sum
         bool ok = true;
@@ -330,11 +336,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             tc::tmem_ld_wait();
             CLK(1, 21);  // read
             const int key0 = pg * PAGE_T + half * 32;
-            if ((pg * PAGE_T + PAGE_T - 1 > pos0) || p.window > 0) {  // a page on the diagonal or at the window's edge
+            if (cap > 0.f) {
+                // cap * tanh(s / cap) with tanh(x) = 1 - 2 / (1 + e^(2x)): one ex2 and one reciprocal
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float r;
+                    const float e = ex2(__uint_as_float(sr[c]) * cap_in) + 1.0f;
+                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e));
+                    sr[c] = __float_as_uint(fmaf(-2.0f * cap, r, cap));
+                }
+            }
+            if ((pg * PAGE_T + PAGE_T - 1 > pos0) || p.window > 0 || p.chunk > 0) {  // a page on the diagonal or at a mask's edge
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const int t = key0 + c;
-                    if (t > pos || (p.window > 0 && t <= pos - p.window)) sr[c] = 0xff800000u;  // -inf
+                    if (t > pos || (p.window > 0 && t <= pos - p.window) || t < chunk_lo) sr[c] = 0xff800000u;  // -inf
                 }
             }
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
@@ -493,14 +509,15 @@ int launch_prefill_tc(const CUtensorMap& mk, const CUtensorMap& mv, const Prefil
 
 }  // namespace
 
-// Same arguments as odin_attention_prefill; the output rows must be 16-byte aligned.
-extern "C" int odin_attention_prefill_tc(const void* q, long long q_row_stride, void* out, long long out_row_stride,
-                                         int n_seqs, int max_new, int Hq, int Hkv, int hd, const void* k_cache,
-                                         const void* v_cache, int n_pages, const int* seq_start,
-                                         const int* seq_len_after, const int* block_table, int bt_stride, int window,
-                                         void* stream) {
+// The output rows must be 16-byte aligned.  chunk > 0: a query sees only the keys of its own chunk of that
+// many positions; scale > 0 replaces 1 / sqrt(hd); softcap > 0: scores become softcap * tanh(score / softcap).
+extern "C" int odin_attention_prefill_tc_masked(const void* q, long long q_row_stride, void* out, long long out_row_stride,
+                                                int n_seqs, int max_new, int Hq, int Hkv, int hd, const void* k_cache,
+                                                const void* v_cache, int n_pages, const int* seq_start,
+                                                const int* seq_len_after, const int* block_table, int bt_stride,
+                                                int window, int chunk, float scale, float softcap, void* stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
-    if (Hkv <= 0 || Hq % Hkv != 0) return ODIN_ERR_BAD_ARG;
+    if (Hkv <= 0 || Hq % Hkv != 0 || chunk < 0 || scale < 0.f || softcap < 0.f) return ODIN_ERR_BAD_ARG;
     if ((q_row_stride % 8) || (((uintptr_t)q) & 15) || (out_row_stride % 8) || (((uintptr_t)out) & 15))
         return ODIN_ERR_UNSUPPORTED;
     CUtensorMap mk, mv;
@@ -515,12 +532,24 @@ extern "C" int odin_attention_prefill_tc(const void* q, long long q_row_stride, 
     p.seq_start = seq_start; p.seq_len_after = seq_len_after;
     p.block_table = block_table; p.bt_stride = bt_stride;
     p.window = window;
-    p.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+    p.chunk = chunk;
+    p.scale_log2 = 1.4426950408889634f * (scale > 0.f ? scale : 1.0f / sqrtf((float)hd));
+    p.cap_log2 = softcap > 0.f ? 1.4426950408889634f * softcap : 0.f;
     p.error = tc_error_flag();
     cudaStream_t s = (cudaStream_t)stream;
     if (hd == 64) return launch_prefill_tc<64>(mk, mv, p, n_seqs, max_new, s);
     if (hd == 128) return launch_prefill_tc<128>(mk, mv, p, n_seqs, max_new, s);
     return ODIN_ERR_UNSUPPORTED;
+}
+
+extern "C" int odin_attention_prefill_tc(const void* q, long long q_row_stride, void* out, long long out_row_stride,
+                                         int n_seqs, int max_new, int Hq, int Hkv, int hd, const void* k_cache,
+                                         const void* v_cache, int n_pages, const int* seq_start,
+                                         const int* seq_len_after, const int* block_table, int bt_stride, int window,
+                                         void* stream) {
+    return odin_attention_prefill_tc_masked(q, q_row_stride, out, out_row_stride, n_seqs, max_new, Hq, Hkv, hd, k_cache,
+                                            v_cache, n_pages, seq_start, seq_len_after, block_table, bt_stride, window,
+                                            0, 0.f, 0.f, stream);
 }
 
 #ifdef ODIN_TRACE

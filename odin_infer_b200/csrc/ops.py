@@ -507,8 +507,10 @@ def attention_decode_scratch(n_tokens: int, n_q: int, head_dim: int, n_split: in
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                      k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
-                     block_table: torch.Tensor, window: int, scratch: torch.Tensor, n_split: int) -> None:
+                     block_table: torch.Tensor, window: int, scratch: torch.Tensor, n_split: int, chunk: int = 0,
+                     scale: float = 0.0, softcap: float = 0.0) -> None:
     """One query token per row over its sequence's bfloat16 cache, keys split n_split ways.
+    chunk, scale, softcap: as `attention_plain` takes them.
 
     The counters on which a launch's key splits meet are one array of the library: all
     decode-attention launches of a process must be ordered on the GPU (one stream, or events
@@ -519,11 +521,11 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, he
     assert q.shape[1] == n_q * head_dim and out.shape == (B, n_q * head_dim)
     assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim) and k_cache.is_contiguous()
     assert scratch.dtype == torch.float32 and scratch.numel() >= attention_decode_scratch(B, n_q, head_dim, n_split)
-    _check(_fn("attention_decode", "odin_attention_decode")(
+    _check(_fn("attention_decode", "odin_attention_decode_masked")(
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE), c_int(k_cache.shape[0]), _ptr(tok_pos),
-        _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window), _ptr(scratch), c_int(n_split),
-        _stream()), "attention_decode", kernels=1 if head_dim in (64, 128) and n_q // n_kv <= 16 else 2)
+        _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window), c_int(chunk), c_float(scale),
+        c_float(softcap), _ptr(scratch), c_int(n_split), _stream()), "attention_decode", kernels=1 if head_dim in (64, 128) and n_q // n_kv <= 16 else 2)
 
 
 def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
@@ -580,7 +582,8 @@ def attention_prefill_supported(head_dim: int) -> bool:
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_q: int, n_kv: int,
                       head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_start: torch.Tensor,
-                      seq_len_after: torch.Tensor, block_table: torch.Tensor, window: int = 0) -> None:
+                      seq_len_after: torch.Tensor, block_table: torch.Tensor, window: int = 0, chunk: int = 0,
+                      scale: float = 0.0, softcap: float = 0.0) -> None:
     """Flash attention of each sequence's new tokens (rows seq_start[b]..seq_start[b+1] of q) over its
     bfloat16 cache, which already holds this step's keys and values: tcgen05.mma with accumulators in
     tensor memory."""
@@ -589,11 +592,11 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: 
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == n_q * head_dim and out.shape == (T, n_q * head_dim)
     assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim) and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert seq_start.dtype == torch.int32 and seq_len_after.dtype == torch.int32 and block_table.dtype == torch.int32
-    _check(_fn("attention_prefill", "odin_attention_prefill_tc")(
+    _check(_fn("attention_prefill", "odin_attention_prefill_tc_masked")(
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(n_seqs), c_int(max_new),
         c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(k_cache.shape[0]),
         _ptr(seq_start), _ptr(seq_len_after), _ptr(block_table), c_int(block_table.stride(0)), c_int(window),
-        _stream()), "attention_prefill")
+        c_int(chunk), c_float(scale), c_float(softcap), _stream()), "attention_prefill")
 
 
 def attention_prefill_check() -> None:

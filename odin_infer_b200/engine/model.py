@@ -36,6 +36,7 @@ class DecoderModel:
                 if p.name not in seen:
                     seen.add(p.name)
                     out.append(p)
+        out += [ParamSpec(n, (), optional=True) for n in self.spec.tolerated_tensors if n not in seen]
         return out
 
     def kernel_groups(self) -> set[str]:

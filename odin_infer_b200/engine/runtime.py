@@ -247,22 +247,20 @@ class Runtime:
                   scale: float = 0.0, softcap: float = 0.0, v_head_dim: int | None = None) -> None:
         """bfloat16: one token per sequence goes to the split-key kernel, prompts (and pieces
         of prompts) to the flash kernel.  The 32-bit path and head sizes that the fast
-        kernels refuse go to the plain kernel, and so does whatever those kernels do not know:
-        a chunk mask, a scale of its own, a cap on the scores, value heads of another size."""
-        if chunk or scale or softcap or (v_head_dim or head_dim) != head_dim:
-            ops.attention_plain(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
-                                window, chunk, scale, softcap, v_head_dim)
-            return
-        if self.dtype == torch.bfloat16 and step.all_single and ops.attention_decode_supported(head_dim):
+        kernels refuse go to the plain kernel, and so do value heads of another size than the keys'.
+        chunk, scale, softcap: a chunk mask, a factor on q . k other than 1 / sqrt(head_dim), a cap on
+        the scores; every kernel takes them."""
+        same_heads = (v_head_dim or head_dim) == head_dim   # the fast kernels' value heads have the keys' size
+        if self.dtype == torch.bfloat16 and same_heads and step.all_single and ops.attention_decode_supported(head_dim):
             B = q.shape[0]
             n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms)
             scratch = self.empty(ops.attention_decode_scratch(B, n_q, head_dim, n_split), dtype=torch.float32)
             ops.attention_decode(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
-                                 window, scratch, n_split)
+                                 window, scratch, n_split, chunk, scale, softcap)
             return
-        if self.dtype == torch.bfloat16 and not step.all_single and ops.attention_prefill_supported(head_dim):
+        if self.dtype == torch.bfloat16 and same_heads and not step.all_single and ops.attention_prefill_supported(head_dim):
             ops.attention_prefill(q, out, step.n_seq_cap, step.max_new, n_q, n_kv, head_dim, k_line, v_line,
-                                  step.seq_start, step.seq_len_after, block_table, window)
+                                  step.seq_start, step.seq_len_after, block_table, window, chunk, scale, softcap)
             return
         ops.attention_plain(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
-                            window)
+                            window, chunk, scale, softcap, v_head_dim)

@@ -41,13 +41,15 @@ class ParamSpec:
     (int32 zeros).  alias_of: the name of another tensor that stands in when this one is
     absent (a tied head).  A dimension of -1 in `shape` takes whatever the model folder
     holds (a size that no configuration key gives); `shape_if_random` is then the shape
-    that random-weights mode writes.
+    that random-weights mode writes.  optional: a tensor that a folder may hold or lack; no part
+    reads it and random-weights mode does not write it.
     """
     name: str
     shape: tuple[int, ...]
     init: str = "matrix"
     alias_of: str | None = None
     shape_if_random: tuple[int, ...] | None = None
+    optional: bool = False
 
     def matches(self, shape) -> bool:
         shape = tuple(shape)

@@ -29,3 +29,4 @@ class ModelSpec:
     head: PartSpec
     max_positions: int = 0                    # 0: no limit of the model's own
     stop_token_ids: tuple[int, ...] = ()
+    tolerated_tensors: tuple[str, ...] = ()   # names a folder may hold although no part reads them

@@ -33,6 +33,8 @@ def check_folder(files: ModelFiles, specs: list[ParamSpec]) -> dict[str, str]:
     missing, wrong = [], []
     source: dict[str, str] = {}
     for s in specs:
+        if s.optional:
+            continue
         if s.name in have:
             src = s.name
         elif s.alias_of is not None and (s.alias_of in have):
@@ -80,6 +82,8 @@ def load_weights(folder: str, specs: list[ParamSpec], compute_dtype: torch.dtype
     by_source: dict[str, torch.Tensor] = {}
     out: dict[str, torch.Tensor] = {}
     for s in specs:
+        if s.optional:
+            continue
         src = source[s.name]
         if src not in by_source:
             t = files.tensor(src)

@@ -131,7 +131,7 @@ def model_param_specs(config: ModelConfig) -> list[ParamSpec]:
     spec = lookup_architecture(config.architecture).build_spec(config)
     params = DecoderModel(spec).params()
     names = {p.name for p in params}
-    return [p for p in params if not (p.alias_of is not None and p.alias_of in names)]
+    return [p for p in params if not p.optional and not (p.alias_of is not None and p.alias_of in names)]
 
 
 def write_random_model(folder: str, config: ModelConfig, seed: int, dtype: torch.dtype = torch.bfloat16) -> str:
@@ -158,11 +158,11 @@ def random_weights(specs: list[ParamSpec], seed: int, compute_dtype: torch.dtype
     out: dict[str, torch.Tensor] = {}
     names = {p.name for p in specs}
     for p in specs:
-        if p.alias_of is not None and p.alias_of in names:
+        if p.optional or (p.alias_of is not None and p.alias_of in names):
             continue
         t = random_tensor(p, seed, stored_dtype, device=device)
         out[p.name] = t if p.is_integer else t.to(torch.float32 if compute_dtype == torch.float32 else t.dtype)
     for p in specs:
-        if p.name not in out:
+        if p.name not in out and not p.optional:
             out[p.name] = out[p.alias_of]
     return out

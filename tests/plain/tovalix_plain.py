@@ -82,6 +82,8 @@ def rotate_half(v: torch.Tensor, positions: torch.Tensor, rot_dims: int, base: f
     """v: [n, heads, dim]; the first rot_dims of every head are turned, element i with element
     i + rot_dims/2 by the angle p * base^(-2i/rot_dims); the rest is kept."""
     half = rot_dims // 2
+    if half == 0:
+        return v
     i = torch.arange(half, dtype=F64)
     ang = positions.to(F64)[:, None] * base ** (-2.0 * i / rot_dims)
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
@@ -92,7 +94,7 @@ def rotate_half(v: torch.Tensor, positions: torch.Tensor, rot_dims: int, base: f
 def attention_keys_values(h: torch.Tensor, m: dict, w: dict, p: str, eps: float):
     """What an attention layer keeps per token: keys after rotation and unit norm, and values."""
     n = h.shape[0]
-    G, dk, dv = m["kv_heads"], m["dim"], m["vdim"]
+    G, dk, dv = m["kv_heads"], m["dim"], m.get("vdim", m["dim"])
     pos = torch.arange(n)
     k = (h @ w[p + "k"].t() + w[p + "k.b"]).reshape(n, G, dk)
     k = unit(rotate_half(k, pos, m["rot"]["dims"], m["rot"]["base"]), eps)
@@ -100,26 +102,37 @@ def attention_keys_values(h: torch.Tensor, m: dict, w: dict, p: str, eps: float)
     return k, v
 
 
-def attention_mixer(h: torch.Tensor, m: dict, w: dict, p: str, eps: float, kv) -> torch.Tensor:
-    """kv: the (keys, values) this layer looks at (its own, or another layer's)."""
-    n = h.shape[0]
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    pos = torch.arange(n)
-    q = (h @ w[p + "q"].t() + w[p + "q.b"]).reshape(n, H, dk)
-    q = unit(rotate_half(q, pos, m["rot"]["dims"], m["rot"]["base"]), eps)
-    k, v = kv
-    cap, chunk = m.get("softcap"), (m.get("mask") or {}).get("size")
-    out = torch.zeros(n, H, dv, dtype=F64)
+def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, cap, chunk, first_pos: int = 0,
+           window=None) -> torch.Tensor:
+    """q: [n, H, dk], the queries of positions first_pos .. first_pos + n - 1; k: [m, G, dk] and v: [m, G, dv],
+    the keys and values of positions 0 .. m - 1.  Position p sees the keys j <= p of its own chunk
+    (j // chunk == p // chunk), and with a window only those with j > p - window; scores q.k * scale,
+    then cap * tanh(score / cap), then a softmax."""
+    n, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(n, H, v.shape[2], dtype=q.dtype)
     for head in range(H):
         g = head // (H // G)
         for t in range(n):
-            lo = (t // chunk) * chunk if chunk else 0
-            s = (k[lo:t + 1, g] @ q[t, head]) * m["scale"]
+            pos = first_pos + t
+            lo = (pos // chunk) * chunk if chunk else 0
+            if window:
+                lo = max(lo, pos - window + 1)
+            s = (k[lo:pos + 1, g] @ q[t, head]) * scale
             if cap:
                 s = cap * torch.tanh(s / cap)
-            a = torch.softmax(s, dim=0)
-            out[t, head] = a @ v[lo:t + 1, g]
-    return out.reshape(n, H * dv) @ w[p + "o"].t() + w[p + "o.b"]
+            out[t, head] = torch.softmax(s, dim=0) @ v[lo:pos + 1, g]
+    return out
+
+
+def attention_mixer(h: torch.Tensor, m: dict, w: dict, p: str, eps: float, kv) -> torch.Tensor:
+    """kv: the (keys, values) this layer looks at (its own, or another layer's)."""
+    n = h.shape[0]
+    H, dk = m["heads"], m["dim"]
+    q = (h @ w[p + "q"].t() + w[p + "q.b"]).reshape(n, H, dk)
+    q = unit(rotate_half(q, torch.arange(n), m["rot"]["dims"], m["rot"]["base"]), eps)
+    out = attend(q, kv[0], kv[1], m["scale"], m.get("softcap"), (m.get("mask") or {}).get("size"))
+    return out.reshape(n, -1) @ w[p + "o"].t() + w[p + "o.b"]
 
 
 def wkv_mixer(h: torch.Tensor, m: dict, w: dict, p: str, eps: float) -> torch.Tensor:
