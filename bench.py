@@ -270,6 +270,216 @@ def other_workload(which: str) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------------------------------------------
+# --workload tovalix: the Tovalix design beside the Qwen3 dense decoder at equal sizes
+# --------------------------------------------------------------------------------------------------------------
+TOVALIX_SIZES = {
+    # width, ff, attention heads / kv heads / head size, recurrence heads x sizes, token input, layers
+    "2048": dict(width=2048, ff=6144, heads=16, kv=8, hd=128, wkv_heads=32, wkv_dim=64, hg_heads=16, hg_dim=128, hg_v=128,
+                 side=256, layers=8, vocab=32768, chunk=1024, rank=64),
+    "4096": dict(width=4096, ff=12288, heads=32, kv=8, hd=128, wkv_heads=64, wkv_dim=64, hg_heads=32, hg_dim=128, hg_v=128,
+                 side=256, layers=4, vocab=32768, chunk=1024, rank=128),
+}
+
+
+def tovalix_config(z: dict) -> dict:
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5, "softcap": 30.0,
+           "rot": {"dims": z["hd"], "base": 1e6}, "mask": {"size": z["chunk"]}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    cycle = [("attention", att), ("wkv", {"heads": z["wkv_heads"], "dim": z["wkv_dim"], "decay_rank": z["rank"]}),
+             ("hgrn2", {"heads": z["hg_heads"], "dim": z["hg_dim"], "vdim": z["hg_v"]}), ("attention", dict(att, kv_from=0))]
+    layers = []
+    for i in range(z["layers"]):
+        kind, mixer = cycle[i % 4]
+        if "kv_from" in mixer:
+            mixer = dict(mixer, kv_from=i - 3)
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Tovalix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 2},
+            "token_side": {"dim": z["side"]}, "layers": layers}
+
+
+def qwen3_config_like(z: dict) -> dict:
+    return dict(architectures=["Qwen3ForCausalLM"], hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=z["layers"],
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["hd"], vocab_size=z["vocab"],
+                rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)
+
+
+def _timed(fn, flush, reps=5, inner=1):
+    """Median device time of fn() in microseconds, L2 flushed before every run."""
+    import torch
+    times = []
+    for r in range(reps + 2):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(inner):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        if r >= 2:
+            times.append(a.elapsed_time(b) * 1e3 / inner)
+    return statistics.median(times)
+
+
+def tovalix_kernels(z: dict, T: int, peaks: dict) -> dict:
+    """Every kernel that the design adds, alone at this size for T token rows (one sequence of T tokens, or T
+    sequences of one token after a context of 512), beside the like kernel of the Qwen3 decoder; microseconds,
+    and the algorithmic bytes (or FLOPs) over the time as a fraction of the measured copy bandwidth (or cuBLAS rate)."""
+    import torch
+    from odin_infer_b200.csrc import ops
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    d, ff = z["width"], z["ff"]
+    decode = T <= 64
+    out = {}
+    def _timed_replayed(fn, flush, reps=5, inner=20):
+        """Kernels of a few rows: `inner` launches captured in a CUDA graph and replayed, so that the device's time is
+        read and not the host's time to launch (their data is far smaller than L2 in any case)."""
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        return _timed(graph.replay, flush, reps) / inner
+    timed = _timed_replayed if decode else _timed
+
+    def note(name, us, nbytes=None, flops=None):
+        rec = {"us": round(us, 1)}
+        if nbytes is not None:
+            rec["of_hbm"] = round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            rec["of_bf16"] = round(flops / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 3)
+        out[name] = rec
+
+    x = torch.randn(T, d, device=dev)
+    delta = torch.randn(T, d, device=dev)
+    w = torch.ones(d, dtype=bf, device=dev)
+    h = torch.empty(T, d, dtype=bf, device=dev)
+    row_bytes = T * d * (4 + 4 + 4 + 2)
+    note("norm: add + RMSNorm (Qwen3)", timed(lambda: ops.add_rmsnorm(x, delta, w, 1e-5, h), flush), row_bytes)
+    note("norm: add + RMSNorm in 2 groups", timed(lambda: ops.row_update(x, delta, None, w, 1e-5, 2, h), flush), row_bytes)
+    note("token input: settle + convert", timed(lambda: ops.row_update(x, delta, None, None, 0.0, 1, h, normalise=False), flush), row_bytes)
+    note("token input: x += w * unit(y)", timed(lambda: ops.normed_add(x, delta, w, 1e-5), flush), T * d * 12)
+    gu = torch.randn(T, 2 * ff, device=dev).to(bf)
+    act = torch.empty(T, ff, dtype=bf, device=dev)
+    pq = torch.tensor([0.3, -0.2], dtype=bf, device=dev)
+    note("feed-forward: SwiGLU (Qwen3)", timed(lambda: ops.swiglu(gu, act), flush), T * ff * 6)
+    note("feed-forward: xIELU", timed(lambda: ops.activation(gu[:, :ff], "xielu", act, pq), flush), T * ff * 4)
+    sd = z["side"]
+    gate = torch.randn(T, sd, device=dev)
+    table = torch.randn(z["vocab"], sd * z["layers"], device=dev).to(bf)
+    ids = torch.randint(0, z["vocab"], (T,), dtype=torch.int32, device=dev)
+    g_out = torch.empty(T, sd, dtype=bf, device=dev)
+    note("token input: gelu(gate) * table row", timed(lambda: ops.gated_lookup(gate, "gelu_tanh", table, sd, ids, g_out), flush), T * sd * 8)
+
+    # sequences: one of T tokens (prompt) or T of one token each
+    n_seq = T if decode else 1
+    starts = torch.arange(0, T + 1, 1 if decode else T, dtype=torch.int32, device=dev)
+    slots = torch.arange(n_seq, dtype=torch.int32, device=dev)
+    seq = (torch.arange(T, dtype=torch.int32, device=dev) if decode else torch.zeros(T, dtype=torch.int32, device=dev))
+    mu = torch.rand(5, d, device=dev).to(bf)
+    streams = torch.empty(5, T, d, dtype=bf, device=dev)
+    for name, mode, H, dk, dv in (("wkv", "bonus", z["wkv_heads"], z["wkv_dim"], z["wkv_dim"]),
+                                  ("hgrn2", "gated", z["hg_heads"], z["hg_dim"], z["hg_v"])):
+        n_state = H * dk * dv
+        state = torch.zeros(n_seq, n_state + d, device=dev)
+        q, k, g = (torch.randn(T, H * dk, device=dev) for _ in range(3))
+        v, o = torch.randn(T, H * dv, device=dev), torch.empty(T, H * dv, device=dev)
+        c0, c1 = torch.randn(H * dk, dtype=bf, device=dev) - 2, torch.rand(H * dk, dtype=bf, device=dev)
+        nbytes = 4 * (T * H * (3 * dk + 2 * dv) + 2 * n_seq * n_state)
+        flops = 5 * T * H * dk * dv
+        us = timed(lambda: ops.linear_recurrence(mode, q, k if mode == "bonus" else None, g, v, c0, c1, o, state[:, :n_state],
+                                                  starts, slots, n_seq, H, dk, dv), flush)
+        note(f"{name}: recurrence ({H} heads of {dk} x {dv})", us, nbytes)
+        out[f"{name}: recurrence ({H} heads of {dk} x {dv})"]["gflops"] = round(flops / us / 1e3, 1)
+        y = torch.empty(T, H * dv, dtype=bf, device=dev)
+        wn = torch.ones(H * dv, dtype=bf, device=dev)
+        note(f"{name}: head norm, weight" + (", gate" if mode == "bonus" else ""),
+             timed(lambda: ops.head_unit_scale(o, wn, True, g if (mode == "bonus" and dk == dv) else None, 1e-5, y, H, dv), flush),
+             T * H * dv * (4 + 2 + (4 if mode == "bonus" else 0)))
+        if mode == "bonus":
+            note("wkv: token shift (5 streams)", timed(lambda: ops.token_shift(h, state[:, n_state:], mu, streams, seq, starts, slots), flush),
+                 T * d * 2 * 6)
+
+    # attention: 512 tokens of context before the T rows when decoding, one prompt of T tokens else
+    Hq, Hkv, hd = z["heads"], z["kv"], z["hd"]
+    ctx = 512 if decode else 0
+    per_seq = (ctx + 1 + 63) // 64 if decode else (T + 63) // 64
+    n_pages = n_seq * per_seq
+    kc = torch.randn(n_pages, Hkv, 64, hd, device=dev).to(bf)
+    vc = torch.randn(n_pages, Hkv, 64, hd, device=dev).to(bf)
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(n_seq, per_seq)
+    pos = (torch.full((T,), ctx, dtype=torch.int32, device=dev) if decode else torch.arange(T, dtype=torch.int32, device=dev))
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * hd, device=dev).to(bf)
+    bias = torch.randn((Hq + 2 * Hkv) * hd, device=dev).to(bf)
+    qn = torch.ones(hd, dtype=bf, device=dev)
+    cos = torch.randn(max(T, ctx + 1), hd // 2, device=dev)
+    q_out = torch.empty(T, Hq * hd, dtype=bf, device=dev)
+    hp_bytes = T * (Hq + 2 * Hkv) * hd * 4
+    note("attention: head preparation (Qwen3)", timed(lambda: ops.head_prep(qkv, Hq, Hkv, hd, qn, qn, 1e-6, cos, cos, hd, pos, seq, bt, kc, vc, q_out=q_out), flush), hp_bytes)
+    note("attention: head preparation (bias, unit norm after rotation)",
+         timed(lambda: ops.head_prep(qkv, Hq, Hkv, hd, None, None, 1e-5, cos, cos, hd, pos, seq, bt, kc, vc, q_out=q_out, bias=bias,
+                                      unit_norm_after=True), flush), hp_bytes)
+    ao = torch.empty(T, Hq * hd, dtype=bf, device=dev)
+    if decode:
+        n_split = 4
+        scratch = torch.empty(ops.attention_decode_scratch(T, Hq, hd, n_split), device=dev)
+        kv_bytes = 2 * 2 * T * Hkv * hd * (ctx + 1)
+        note("attention: decode over 512 keys (Qwen3)", timed(lambda: ops.attention_decode(q_out, ao, Hq, Hkv, hd, kc, vc, pos, seq, bt, 0, scratch, n_split), flush), kv_bytes)
+        note("attention: decode over 512 keys, chunk + capped scores",
+             timed(lambda: ops.attention_decode(q_out, ao, Hq, Hkv, hd, kc, vc, pos, seq, bt, 0, scratch, n_split, z["chunk"], hd ** -0.5, 30.0), flush), kv_bytes)
+    else:
+        lens = torch.tensor([T], dtype=torch.int32, device=dev)
+        full = 4 * Hq * hd * (T * (T + 1) // 2)
+        c = z["chunk"]
+        inside = sum(min(c, T - a) * (min(c, T - a) + 1) // 2 for a in range(0, T, c)) * 4 * Hq * hd
+        note("attention: prompt (Qwen3)", timed(lambda: ops.attention_prefill(q_out, ao, 1, T, Hq, Hkv, hd, kc, vc, starts, lens, bt, 0), flush), flops=full)
+        note("attention: prompt, capped scores", timed(lambda: ops.attention_prefill(q_out, ao, 1, T, Hq, Hkv, hd, kc, vc, starts, lens, bt, 0, 0, hd ** -0.5, 30.0), flush), flops=full)
+        note(f"attention: prompt, chunks of {c} + capped scores",
+             timed(lambda: ops.attention_prefill(q_out, ao, 1, T, Hq, Hkv, hd, kc, vc, starts, lens, bt, 0, c, hd ** -0.5, 30.0), flush), flops=inside)
+    ops.attention_prefill_check()
+    ops.attention_decode_check()
+    return out
+
+
+def tovalix_workload(steps: int, warmup: int) -> int:
+    """The Tovalix design at two sizes that resemble a real model's layers, beside the Qwen3 dense decoder of the same
+    width, feed-forward size, attention heads, number of layers and vocabulary (random weights): a prompt of 2,048
+    tokens in one step, decoding at batch 8 after 512-token prompts (device-timed), and every new kernel alone."""
+    import torch
+    from odin_infer_b200 import Engine, Engine_Opts
+    from odin_infer_b200.config import config_from_dict
+    from odin_infer_b200.csrc import ops
+    peaks, peak_source = load_peaks()
+    result = {"metric": "Tovalix beside the Qwen3 dense decoder at equal sizes: prompt of 2,048 tokens, decode at batch 8 "
+                        "(512-token prompts), bf16, random weights", "peak_source": peak_source, "sizes": {}}
+    steps = min(steps, 64)
+    for name, z in TOVALIX_SIZES.items():
+        entry = {}
+        for model, raw in (("tovalix", tovalix_config(z)), ("qwen3", qwen3_config_like(z))):
+            need = PROMPT + warmup + steps + 72
+            engine = Engine.random(config_from_dict(raw), WEIGHT_SEED, Engine_Opts(
+                max_ctx=CONTEXT, max_tokens=max(8 * ((need + 63) // 64 * 64), PREFILL_TOKENS + 64), max_batch=8,
+                dtype="bfloat16", verbose=False))
+            ms_pf = run_prefill(engine, z["vocab"])
+            tps, ms_step, _, launches = run_decode(engine, 8, steps, warmup, z["vocab"])
+            entry[model] = {"layers": z["layers"], "weights_gib": round(engine.weight_bytes / 2 ** 30, 2),
+                            "prefill_2048": {"ms": round(ms_pf, 3), "tokens_per_s": round(PREFILL_TOKENS / ms_pf * 1e3)},
+                            "decode_b8": {"ms_per_step": round(ms_step, 4), "tokens_per_s": round(tps, 1),
+                                          "weights_over_time_of_hbm": round(engine.weight_bytes / (ms_step / 1e3) / 1e9 / peaks["hbm_gbs"], 3),
+                                          "launches_per_step": launches // steps}}
+            engine.destroy()
+            del engine
+            torch.cuda.empty_cache()
+        entry["kernels_prompt_2048_rows"] = tovalix_kernels(z, PREFILL_TOKENS, peaks)
+        entry["kernels_decode_8_rows"] = tovalix_kernels(z, 8, peaks)
+        result["sizes"][name] = entry
+    ops.gemm_tc_check()
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -281,10 +491,11 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for profilers)")
-    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long", "tovalix"],
                     help="8b: the contract's run (default).  The others are further workloads of the baseline's list and "
                          "print a line of their own: 1.7b-mixed = Qwen3-1.7B shape, 64 prompts of 16..2048 tokens, 128 new "
-                         "tokens each; 32b-long = Qwen3-32B shape, a 2,048-token prompt, decoding 1 and 8 sequences at context 8192")
+                         "tokens each; 32b-long = Qwen3-32B shape, a 2,048-token prompt, decoding 1 and 8 sequences at context 8192; "
+                         "tovalix = the Tovalix design beside the Qwen3 decoder at equal sizes, and its kernels alone")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -296,6 +507,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(args.warmup, 3)
+    if args.workload == "tovalix":
+        return tovalix_workload(args.steps, warmup)
     if args.workload != "8b":
         return other_workload(args.workload)
 

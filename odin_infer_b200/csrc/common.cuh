@@ -33,7 +33,34 @@ struct VecRef {
     __device__ __forceinline__ float at(int i) const {
         return is_bf16 ? __bfloat162float(((const bf16*)p)[i]) : ((const float*)p)[i];
     }
+    // elements i .. i + 3 (i a multiple of 4, the vector 16-byte aligned)
+    __device__ __forceinline__ float4 at4(int i) const {
+        if (is_bf16) {
+            const uint2 v = *reinterpret_cast<const uint2*>((const bf16*)p + i);
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+            return make_float4(a.x, a.y, b.x, b.y);
+        }
+        return *reinterpret_cast<const float4*>((const float*)p + i);
+    }
 };
+
+// Four consecutive elements as one 16-byte (32-bit) or 8-byte (bfloat16) access; the address is that much aligned.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -11,14 +11,14 @@
 //   * the per-head unit norm of the recurrence's output, times a weight, times an optional gate.
 //
 // The state lives in 32-bit floats in the engine's per-sequence state area and is carried from
-// step to step; a sequence's tokens are walked in order by one CTA per (sequence, head), thread j
-// owning column j of S in registers, so the result does not depend on how the tokens were cut into
+// step to step; a sequence's tokens are walked in order by one CTA per (sequence, head), column j of S
+// held in the registers of four lanes, so the result does not depend on how the tokens were cut into
 // steps or on what else is in the batch.  Decays, gates, exponentials and the state are 32-bit.
 #include "common.cuh"
 
 // ------------------------------------------------------------ token shift
 // out[s][t][:] = h[t] + (prev - h[t]) * mu[s], s < n_mix.  Rows of sequence -1 are skipped.
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 token_shift_kernel(const T* __restrict__ h, const float* __restrict__ state, size_t state_stride, VecRef mu, int n_mix,
                    T* __restrict__ out, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
@@ -31,7 +31,19 @@ token_shift_kernel(const T* __restrict__ h, const float* __restrict__ state, siz
     pdl_wait();
     if (seq < 0) return;
     const T* hr = h + (size_t)t * d;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    if (VEC) {  // the width a multiple of four, every row 16-byte aligned
+        for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+            const float4 hv = ld4(hr + c);
+            const float4 pv = (t == first) ? ld4(state + (size_t)slot * state_stride + c) : ld4(hr + c - d);
+            const float4 diff = make_float4(pv.x - hv.x, pv.y - hv.y, pv.z - hv.z, pv.w - hv.w);
+            for (int s = 0; s < n_mix; ++s) {
+                const float4 m = mu.at4(s * d + c);
+                st4(out + ((size_t)s * n_rows + t) * d + c,
+                    make_float4(hv.x + diff.x * m.x, hv.y + diff.y * m.y, hv.z + diff.z * m.z, hv.w + diff.w * m.w));
+            }
+        }
+    }
+    for (int c = threadIdx.x; !VEC && c < d; c += blockDim.x) {
         const float hv = to_f32(hr[c]);
         const float pv = (t == first) ? state[(size_t)slot * state_stride + c] : to_f32(hr[c - d]);
         const float diff = pv - hv;
@@ -47,12 +59,14 @@ extern "C" int odin_token_shift(const void* h, int dtype, const float* state, lo
     if (d <= 0 || n_mix <= 0) return ODIN_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     VecRef mv{mu, mu_dtype == ODIN_BF16};
+    const bool vec = (d % 4 == 0) && (state_stride % 4 == 0) &&
+                     ((((uintptr_t)h) | ((uintptr_t)state) | ((uintptr_t)mu) | ((uintptr_t)out)) % 16 == 0);
     if (dtype == ODIN_BF16)
-        odin_launch(token_shift_kernel<bf16>, dim3(n_rows), dim3(256), 0, s, (const bf16*)h, state, (size_t)state_stride,
-                    mv, n_mix, (bf16*)out, tok_seq, seq_start, seq_slots, n_rows, d);
+        odin_launch(vec ? token_shift_kernel<bf16, true> : token_shift_kernel<bf16, false>, dim3(n_rows), dim3(256), 0, s,
+                    (const bf16*)h, state, (size_t)state_stride, mv, n_mix, (bf16*)out, tok_seq, seq_start, seq_slots, n_rows, d);
     else if (dtype == ODIN_F32)
-        odin_launch(token_shift_kernel<float>, dim3(n_rows), dim3(256), 0, s, (const float*)h, state, (size_t)state_stride,
-                    mv, n_mix, (float*)out, tok_seq, seq_start, seq_slots, n_rows, d);
+        odin_launch(vec ? token_shift_kernel<float, true> : token_shift_kernel<float, false>, dim3(n_rows), dim3(256), 0, s,
+                    (const float*)h, state, (size_t)state_stride, mv, n_mix, (float*)out, tok_seq, seq_start, seq_slots, n_rows, d);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();
@@ -62,7 +76,10 @@ extern "C" int odin_token_shift(const void* h, int dtype, const float* state, lo
 // ------------------------------------------------------------ the recurrence
 #define REC_BONUS 0   // o = (S + diag(u) k v^T)^T r, then S = diag(w) S + k v^T, w = exp(-exp(raw + w0))
 #define REC_GATED 1   // f = l + (1 - l) sigmoid(raw + b); S = diag(f) S + (1 - f) v^T; o = S^T silu(q)
-#define REC_TOKENS 8  // tokens whose q, k, w are staged in shared memory together
+// Threads that share a column of S: each owns a quarter of the key channels.  (Sixteen lanes per column, a quarter of
+// the registers each, walked a prompt of 2,048 tokens a fifth faster and made a decode step three to four times slower:
+// four times the threads for the same work.)
+#define REC_SPLIT 4
 #define REC_MAX_DK 256
 
 struct RecParams {
@@ -79,81 +96,140 @@ struct RecParams {
     const void* shift_src; int shift_is_bf16; float* shift_state; long long shift_stride; int width;
 };
 
-template <int DK, int MODE>
-__global__ void __launch_bounds__(256)
+// One CTA per (sequence, head) walks the sequence's tokens in order.  Column j of S belongs to REC_SPLIT lanes of
+// one warp (lane = part * 8 + j % 8), each holding SL consecutive key channels of it in registers; a token costs
+// each thread SL multiply-adds for the output and SL for the state, and the column's output is the sum of its
+// parts' shares (two shuffles), always added in the same order.  The tokens' q, k, decays and values are prepared a
+// block of tokens at a time in shared memory (the exponentials once per token and channel, not once per column);
+// the next block's inputs are fetched into registers before the current block is walked, so that the walk itself
+// reads shared memory only.
+// A CTA covers `cols` columns (a multiple of 8, at most REC_COLS; blockIdx.z takes the next ones), so that it never
+// has more than 512 threads and the state fits the registers; the launcher takes fewer columns per CTA when there
+// are few (sequence, head) pairs, so that a long prompt of one sequence still occupies the GPU.  A column's
+// arithmetic does not depend on which CTA holds it.
+#define REC_COLS 128
+#define REC_FETCH 4   // elements of each input that a thread fetches ahead per block of tokens
+template <int SL, int MODE>
+__global__ void __launch_bounds__(REC_COLS * REC_SPLIT)
 linear_recurrence_kernel(RecParams p) {
-    constexpr int NK = DK > 0 ? DK : REC_MAX_DK;
-    __shared__ float sq[REC_TOKENS][NK], sk[REC_TOKENS][NK], sw[REC_TOKENS][NK];
+    constexpr int NK = SL * REC_SPLIT;             // key channels the registers hold (dk <= NK)
+    constexpr int TOK = NK > 128 ? 8 : 16;
+    constexpr bool BONUS_IN_REGS = SL <= 32;
+    __shared__ __align__(16) float sq[TOK][NK], sk[TOK][NK], sw[TOK][NK];
+    __shared__ float sv[TOK][REC_COLS], sb[NK];
     pdl_trigger();
-    const int b = blockIdx.x, head = blockIdx.y, j = threadIdx.x;
-    const int dk = DK > 0 ? DK : p.dk;
+    const int b = blockIdx.x, head = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int ccols = blockDim.x / REC_SPLIT;      // columns of this CTA
+    const int part = lane >> 3, cj = warp * 8 + (lane & 7), j = blockIdx.z * ccols + cj;
+    const int dk = p.dk;
     const int row0 = p.seq_start[b], row1 = p.seq_start[b + 1];
     const int slot = p.seq_slots[b];
+    const int hc = head * dk;
+    const int tok = max(1, min(TOK, REC_FETCH * (int)blockDim.x / NK));   // tokens per block: what the threads can fetch ahead
+    for (int i = threadIdx.x; i < NK; i += blockDim.x) sb[i] = (MODE == REC_BONUS && i < dk) ? p.c1.at(hc + i) : 0.f;
     pdl_wait();
     if (row1 <= row0) return;  // an empty (padding) sequence owns no state
     const bool owns = j < p.dv;
-    float S[NK];
+    const int i0 = part * SL;
+    float S[SL], ub[BONUS_IN_REGS ? SL : 1];
     float* st = p.state + (size_t)slot * p.state_stride + (size_t)head * dk * p.dv + j;
-    if (owns) {
 #pragma unroll
-        for (int i = 0; i < NK; ++i)
-            if (i < dk) S[i] = st[(size_t)i * p.dv];
+    for (int i = 0; i < SL; ++i) S[i] = (owns && i0 + i < dk) ? st[(size_t)(i0 + i) * p.dv] : 0.f;
+    __syncthreads();
+    if (BONUS_IN_REGS) {
+#pragma unroll
+        for (int i = 0; i < SL; ++i) ub[i] = sb[i0 + i];
     }
-    const int hc = head * dk;
-    for (int t0 = row0; t0 < row1; t0 += REC_TOKENS) {
-        const int nt = min(REC_TOKENS, row1 - t0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < nt * dk; e += blockDim.x) {
-            const int u = e / dk, i = e % dk;
-            const size_t r = (size_t)(t0 + u);
-            const float raw = p.g[r * p.g_stride + hc + i];
-            const float qv = p.q[r * p.q_stride + hc + i];
-            if (MODE == REC_BONUS) {
-                sq[u][i] = qv;
-                sk[u][i] = p.k[r * p.k_stride + hc + i];
-                sw[u][i] = expf(-expf(raw + p.c0.at(hc + i)));
-            } else {
-                const float l = p.c1.at(hc + i);
-                const float f = l + (1.0f - l) * (1.0f / (1.0f + expf(-(raw + p.c0.at(hc + i)))));
-                sq[u][i] = qv / (1.0f + expf(-qv));
-                sk[u][i] = 1.0f - f;
-                sw[u][i] = f;
+
+    float rq[REC_FETCH], rk[REC_FETCH], rg[REC_FETCH], rv[REC_FETCH];
+    auto fetch = [&](int t0, int nt) {
+#pragma unroll
+        for (int f = 0; f < REC_FETCH; ++f) {
+            const int e = threadIdx.x + f * blockDim.x;
+            rq[f] = rk[f] = rg[f] = rv[f] = 0.f;
+            if (e < nt * NK) {
+                const int u = e / NK, i = e % NK;
+                if (i < dk) {
+                    const size_t r = (size_t)(t0 + u);
+                    rq[f] = p.q[r * p.q_stride + hc + i];
+                    rg[f] = p.g[r * p.g_stride + hc + i];
+                    if (MODE == REC_BONUS) rk[f] = p.k[r * p.k_stride + hc + i];
+                }
+            }
+            if (e < nt * ccols) {
+                const int u = e / ccols, c = e % ccols, col = blockIdx.z * ccols + c;
+                if (col < p.dv) rv[f] = p.v[(size_t)(t0 + u) * p.v_stride + (size_t)head * p.dv + col];
             }
         }
-        __syncthreads();
-        if (owns) {
-            for (int u = 0; u < nt; ++u) {
-                const size_t r = (size_t)(t0 + u);
-                const float vj = p.v[r * p.v_stride + (size_t)head * p.dv + j];
-                float acc = 0.f;
-                if (MODE == REC_BONUS) {
+    };
+    auto commit = [&](int nt) {
 #pragma unroll
-                    for (int i = 0; i < NK; ++i) {
-                        if (i < dk) {
-                            const float kv = sk[u][i] * vj;
-                            acc = fmaf(sq[u][i], fmaf(p.c1.at(hc + i), kv, S[i]), acc);
-                            S[i] = fmaf(sw[u][i], S[i], kv);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < NK; ++i) {
-                        if (i < dk) {
-                            S[i] = fmaf(sw[u][i], S[i], sk[u][i] * vj);
-                            acc = fmaf(sq[u][i], S[i], acc);
-                        }
+        for (int f = 0; f < REC_FETCH; ++f) {
+            const int e = threadIdx.x + f * blockDim.x;
+            if (e < nt * NK) {
+                const int u = e / NK, i = e % NK;
+                float qv = 0.f, kv = 0.f, wv = 0.f;   // channels beyond dk: nothing in, nothing kept
+                if (i < dk) {
+                    if (MODE == REC_BONUS) {
+                        qv = rq[f];
+                        kv = rk[f];
+                        wv = expf(-expf(rg[f] + p.c0.at(hc + i)));
+                    } else {
+                        const float l = p.c1.at(hc + i);
+                        const float fg = l + (1.0f - l) * (1.0f / (1.0f + expf(-(rg[f] + p.c0.at(hc + i)))));
+                        qv = rq[f] / (1.0f + expf(-rq[f]));
+                        kv = 1.0f - fg;
+                        wv = fg;
                     }
                 }
-                p.o[r * p.o_stride + (size_t)head * p.dv + j] = acc;
+                sq[u][i] = qv; sk[u][i] = kv; sw[u][i] = wv;
             }
+            if (e < nt * ccols) sv[e / ccols][e % ccols] = rv[f];
+        }
+    };
+
+    fetch(row0, min(tok, row1 - row0));
+    for (int t0 = row0; t0 < row1; t0 += tok) {
+        const int nt = min(tok, row1 - t0);
+        __syncthreads();   // the block before has been walked
+        commit(nt);
+        __syncthreads();
+        if (t0 + tok < row1) fetch(t0 + tok, min(tok, row1 - t0 - tok));
+        for (int u = 0; u < nt; ++u) {
+            const float vj = sv[u][cj];
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int i4 = 0; i4 < SL; i4 += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&sk[u][i0 + i4]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&sq[u][i0 + i4]);
+                const float4 w4 = *reinterpret_cast<const float4*>(&sw[u][i0 + i4]);
+                const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = i4 + e;
+                    const float kv = kk[e] * vj;
+                    if (MODE == REC_BONUS) {
+                        const float bonus = BONUS_IN_REGS ? ub[BONUS_IN_REGS ? i : 0] : sb[i0 + i];
+                        const float term = qq[e] * fmaf(bonus, kv, S[i]);
+                        if (e & 1) acc1 += term; else acc0 += term;
+                        S[i] = fmaf(ww[e], S[i], kv);
+                    } else {
+                        S[i] = fmaf(ww[e], S[i], kv);
+                        if (e & 1) acc1 = fmaf(qq[e], S[i], acc1); else acc0 = fmaf(qq[e], S[i], acc0);
+                    }
+                }
+            }
+            float acc = acc0 + acc1;
+            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+            if (owns && part == 0) p.o[(size_t)(t0 + u) * p.o_stride + (size_t)head * p.dv + j] = acc;
         }
     }
-    if (owns) {
 #pragma unroll
-        for (int i = 0; i < NK; ++i)
-            if (i < dk) st[(size_t)i * p.dv] = S[i];
-    }
-    if (head == 0 && p.shift_src != nullptr) {
+    for (int i = 0; i < SL; ++i)
+        if (owns && i0 + i < dk) st[(size_t)(i0 + i) * p.dv] = S[i];
+    if (head == 0 && blockIdx.z == 0 && p.shift_src != nullptr) {
         float* dst = p.shift_state + (size_t)slot * p.shift_stride;
         const size_t last = (size_t)(row1 - 1) * p.width;
         for (int c = threadIdx.x; c < p.width; c += blockDim.x)
@@ -179,22 +255,26 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
     p.shift_src = shift_src; p.shift_is_bf16 = shift_dtype == ODIN_BF16; p.shift_state = shift_state;
     p.shift_stride = shift_stride; p.width = width;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = (dv + 31) / 32 * 32;
-    dim3 grid(n_seqs, H);
-#define GO(DK)                                                                                                  \
+    // columns per CTA: all of them (up to REC_COLS) when (sequence, head) pairs alone fill the GPU twice, else
+    // halved down to 32 until they do
+    int cols = (dv < REC_COLS ? dv : REC_COLS);
+    cols = (cols + 7) / 8 * 8;
+    while (cols > 32 && (cols / 2) % 8 == 0 && (long long)n_seqs * H * ((dv + cols - 1) / cols) < 2 * 148) cols /= 2;
+    const int threads = cols * REC_SPLIT;      // a warp per eight columns
+    dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
+#define GO(SL)                                                                                                  \
     do {                                                                                                        \
-        if (mode == REC_BONUS) odin_launch(linear_recurrence_kernel<DK, REC_BONUS>, grid, dim3(threads), 0, s, p);  \
-        else odin_launch(linear_recurrence_kernel<DK, REC_GATED>, grid, dim3(threads), 0, s, p);                \
+        if (mode == REC_BONUS) odin_launch(linear_recurrence_kernel<SL, REC_BONUS>, grid, dim3(threads), 0, s, p);  \
+        else odin_launch(linear_recurrence_kernel<SL, REC_GATED>, grid, dim3(threads), 0, s, p);                \
     } while (0)
-    switch (dk) {  // the usual sizes keep the state column in registers; any other size up to 256 runs the general kernel
-        case 16: GO(16); break;
-        case 32: GO(32); break;
-        case 48: GO(48); break;
-        case 64: GO(64); break;
-        case 96: GO(96); break;
-        case 128: GO(128); break;
-        default: GO(0); break;
-    }
+    // registers for the smallest multiple of REC_SPLIT channels that holds dk
+    if (dk <= 16) GO(4);
+    else if (dk <= 32) GO(8);
+    else if (dk <= 48) GO(12);
+    else if (dk <= 64) GO(16);
+    else if (dk <= 96) GO(24);
+    else if (dk <= 128) GO(32);
+    else GO(64);
 #undef GO
     ODIN_LAUNCH_CHECK();
     return 0;

@@ -18,7 +18,9 @@
 // row gather.  mode 0: out = w * (x_new / sqrt(mean_g(x_new^2) + eps)) with the mean over the
 // element's own group; out may be x itself (32-bit, in place).  mode 1: out = x_new converted
 // (out may be null: the update alone).
-template <typename TD, typename TO>
+// VEC: the row, a group and every distance between rows and parts are multiples of four elements and every
+// pointer is 16-byte aligned, so everything moves four elements at a time; the same sums in the same order.
+template <typename TD, typename TO, bool VEC>
 __global__ void __launch_bounds__(ROW_THREADS)
 row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t split_stride, VecRef bias, VecRef w,
                   float eps, int groups, int mode, TO* out, const int* __restrict__ rows, int d) {
@@ -38,38 +40,80 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
     float* xr = x + (size_t)src * d;
     const bool updated = delta != nullptr || bias.p != nullptr;
     const bool write_back = updated && rows == nullptr;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        float v = xr[j];
-        if (delta != nullptr)
-            for (int s = 0; s < n_split; ++s) v += to_f32(delta[(size_t)s * split_stride + (size_t)src * d + j]);
-        if (bias.p != nullptr) v += bias.at(j);
-        rowbuf[j] = v;
+    if (VEC) {
+        for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+            float4 v = ld4(xr + j);
+            if (delta != nullptr)
+                for (int s = 0; s < n_split; ++s) {
+                    const float4 dv = ld4(delta + (size_t)s * split_stride + (size_t)src * d + j);
+                    v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+                }
+            if (bias.p != nullptr) {
+                const float4 bv = bias.at4(j);
+                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+            }
+            st4(rowbuf + j, v);
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            float v = xr[j];
+            if (delta != nullptr)
+                for (int s = 0; s < n_split; ++s) v += to_f32(delta[(size_t)s * split_stride + (size_t)src * d + j]);
+            if (bias.p != nullptr) v += bias.at(j);
+            rowbuf[j] = v;
+        }
     }
     __syncthreads();
     if (mode == 1) {
-        for (int j = threadIdx.x; j < d; j += blockDim.x) {
-            const float v = rowbuf[j];
-            if (write_back) xr[j] = v;
-            if (o != nullptr) o[j] = from_f32<TO>(v);
+        if (VEC) {
+            for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+                const float4 v = ld4(rowbuf + j);
+                if (write_back) st4(xr + j, v);
+                if (o != nullptr) st4(o + j, v);
+            }
+        } else {
+            for (int j = threadIdx.x; j < d; j += blockDim.x) {
+                const float v = rowbuf[j];
+                if (write_back) xr[j] = v;
+                if (o != nullptr) o[j] = from_f32<TO>(v);
+            }
         }
         return;
     }
     const int gsz = d / groups;
+    const bool keep = write_back && (void*)out != (void*)x;
     for (int g = 0; g < groups; ++g) {
+        // a thread adds the squares of its elements in the order of their columns, in both variants
         float ss = 0.f;
-        for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
-            const float v = rowbuf[g * gsz + j];
-            ss += v * v;
+        if (VEC) {
+            for (int j = threadIdx.x * 4; j < gsz; j += blockDim.x * 4) {
+                const float4 v = ld4(rowbuf + g * gsz + j);
+                ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+            }
+        } else {
+            for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
+                const float v = rowbuf[g * gsz + j];
+                ss += v * v;
+            }
         }
         ss = block_sum(ss, red);
         ss /= (float)gsz;
         ss += eps;
         const float rs = 1.0f / sqrtf(ss);
-        for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
-            const int c = g * gsz + j;
-            const float v = rowbuf[c];
-            if (write_back && (void*)out != (void*)x) xr[c] = v;
-            o[c] = from_f32<TO>(w.at(c) * (rs * v));
+        if (VEC) {
+            for (int j = threadIdx.x * 4; j < gsz; j += blockDim.x * 4) {
+                const int c = g * gsz + j;
+                const float4 v = ld4(rowbuf + c), wv = w.at4(c);
+                if (keep) st4(xr + c, v);
+                st4(o + c, make_float4(wv.x * (rs * v.x), wv.y * (rs * v.y), wv.z * (rs * v.z), wv.w * (rs * v.w)));
+            }
+        } else {
+            for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
+                const int c = g * gsz + j;
+                const float v = rowbuf[c];
+                if (keep) xr[c] = v;
+                o[c] = from_f32<TO>(w.at(c) * (rs * v));
+            }
         }
     }
 }
@@ -84,9 +128,12 @@ extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int
     if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     VecRef wv{w, w_dtype == ODIN_BF16}, bv{bias, bias_dtype == ODIN_BF16};
+    const int gsz = mode == 0 ? d / groups : d;
+    const bool vec = (d % 4 == 0) && (gsz % 4 == 0) && (split_stride % 4 == 0) &&
+                     ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)bias) | ((uintptr_t)w) | ((uintptr_t)out)) % 16 == 0);
 #define GO(TD, TO)                                                                                               \
     do {                                                                                                         \
-        auto kern = row_update_kernel<TD, TO>;                                                                   \
+        auto kern = vec ? row_update_kernel<TD, TO, true> : row_update_kernel<TD, TO, false>;                    \
         if (smem > 48 * 1024) {                                                                                  \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
             if (e != cudaSuccess) return (int)e;                                                                 \
@@ -104,7 +151,7 @@ extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int
 }
 
 // ------------------------------------------------------------ x += w * (y / rms(y))
-template <typename TY>
+template <typename TY, bool VEC>
 __global__ void __launch_bounds__(ROW_THREADS)
 normed_add_kernel(float* __restrict__ x, const TY* __restrict__ y, int n_split, size_t split_stride, VecRef w, float eps,
                   const int* __restrict__ tok_seq, int d) {
@@ -115,18 +162,39 @@ normed_add_kernel(float* __restrict__ x, const TY* __restrict__ y, int n_split, 
     pdl_wait();
     if (tok_seq != nullptr && tok_seq[r] < 0) return;
     float ss = 0.f;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        float v = 0.f;
-        for (int s = 0; s < n_split; ++s) v += to_f32(y[(size_t)s * split_stride + (size_t)r * d + j]);
-        rowbuf[j] = v;
-        ss += v * v;
+    if (VEC) {
+        for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < n_split; ++s) {
+                const float4 yv = ld4(y + (size_t)s * split_stride + (size_t)r * d + j);
+                v.x += yv.x; v.y += yv.y; v.z += yv.z; v.w += yv.w;
+            }
+            st4(rowbuf + j, v);
+            ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            float v = 0.f;
+            for (int s = 0; s < n_split; ++s) v += to_f32(y[(size_t)s * split_stride + (size_t)r * d + j]);
+            rowbuf[j] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, red);
     ss /= (float)d;
     ss += eps;
     const float rs = 1.0f / sqrtf(ss);
     float* xr = x + (size_t)r * d;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) xr[j] += w.at(j) * (rs * rowbuf[j]);
+    if (VEC) {
+        for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+            const float4 v = ld4(rowbuf + j), wv = w.at4(j);
+            float4 xv = ld4(xr + j);
+            xv.x += wv.x * (rs * v.x); xv.y += wv.y * (rs * v.y); xv.z += wv.z * (rs * v.z); xv.w += wv.w * (rs * v.w);
+            st4(xr + j, xv);
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) xr[j] += w.at(j) * (rs * rowbuf[j]);
+    }
 }
 
 extern "C" int odin_normed_add(float* x, const void* y, int y_dtype, int n_split, long long split_stride, const void* w,
@@ -136,9 +204,10 @@ extern "C" int odin_normed_add(float* x, const void* y, int y_dtype, int n_split
     if (d <= 0 || smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     VecRef wv{w, w_dtype == ODIN_BF16};
+    const bool vec = (d % 4 == 0) && (split_stride % 4 == 0) && ((((uintptr_t)x) | ((uintptr_t)y) | ((uintptr_t)w)) % 16 == 0);
 #define GO(TY)                                                                                                   \
     do {                                                                                                         \
-        auto kern = normed_add_kernel<TY>;                                                                       \
+        auto kern = vec ? normed_add_kernel<TY, true> : normed_add_kernel<TY, false>;                                                                     \
         if (smem > 48 * 1024) {                                                                                  \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
             if (e != cudaSuccess) return (int)e;                                                                 \
@@ -177,7 +246,7 @@ __device__ __forceinline__ float activate(int act, float z, float c0, float c1) 
     }
 }
 
-template <typename TI, typename TO>
+template <typename TI, typename TO, bool VEC>
 __global__ void __launch_bounds__(256)
 activation_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, size_t in_stride, int act, VecRef params,
                   TO* __restrict__ out, size_t out_stride, int T, int n) {
@@ -188,6 +257,21 @@ activation_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, s
         c1 = 0.5f + softplus_f(params.at(1));
     }
     pdl_wait();
+    if (VEC) {  // four elements of a row at a time
+        const int n4 = n / 4;
+        const long long total4 = (long long)T * n4;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+            const int t = (int)(i / n4), c = (int)(i % n4) * 4;
+            float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < n_split; ++s) {
+                const float4 v = ld4(in + (size_t)s * split_stride + (size_t)t * in_stride + c);
+                z.x += v.x; z.y += v.y; z.z += v.z; z.w += v.w;
+            }
+            st4(out + (size_t)t * out_stride + c, make_float4(activate(act, z.x, c0, c1), activate(act, z.y, c0, c1),
+                                                               activate(act, z.z, c0, c1), activate(act, z.w, c0, c1)));
+        }
+        return;
+    }
     const long long total = (long long)T * n;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int t = (int)(i / n), c = (int)(i % n);
@@ -203,12 +287,17 @@ extern "C" int odin_activation(const void* in, int in_dtype, int n_split, long l
     if (T <= 0 || n <= 0) return 0;
     if (act < 0 || act > ACT_XIELU || (act == ACT_XIELU && params == nullptr)) return ODIN_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const long long total = (long long)T * n;
+    const bool vec = (n % 4 == 0) && (in_stride % 4 == 0) && (out_stride % 4 == 0) && (split_stride % 4 == 0) &&
+                     ((((uintptr_t)in) | ((uintptr_t)out)) % 16 == 0);
+    const long long total = (long long)T * n / (vec ? 4 : 1);
     const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
     VecRef pv{params, params_dtype == ODIN_BF16};
 #define GO(TI, TO)                                                                                              \
-    odin_launch(activation_kernel<TI, TO>, dim3(blocks), dim3(256), 0, s, (const TI*)in, n_split,               \
-                (size_t)split_stride, (size_t)in_stride, act, pv, (TO*)out, (size_t)out_stride, T, n)
+    do {                                                                                                        \
+        auto kern = vec ? activation_kernel<TI, TO, true> : activation_kernel<TI, TO, false>;                   \
+        odin_launch(kern, dim3(blocks), dim3(256), 0, s, (const TI*)in, n_split,                                \
+                    (size_t)split_stride, (size_t)in_stride, act, pv, (TO*)out, (size_t)out_stride, T, n);      \
+    } while (0)
     if (in_dtype == ODIN_F32 && out_dtype == ODIN_F32) GO(float, float);
     else if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16) GO(float, bf16);
     else if (in_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(bf16, bf16);
