@@ -128,7 +128,7 @@ attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv,
             for (int e = 0; e < EPL; ++e) s = fmaf(qf[h][e], kf[e], s);
 #pragma unroll
             for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (cap_log2 > 0.f) s = cap_log2 * tanhf(s / cap_log2);
+            if (cap_log2 > 0.f) s = attn::softcap_log2(s, cap_log2);
             if (have) {
                 const float m_new = fmaxf(m[h], s);
                 const float corr = exp2f(m[h] - m_new);

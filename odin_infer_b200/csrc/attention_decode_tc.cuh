@@ -154,7 +154,7 @@ __device__ __forceinline__ void attend_page(const uint32_t sK_u, const uint32_t 
         for (int j = 0; j < 4; ++j) {
             const int tk = key0 + nb * 8 + (j & 1);
             float v = s[nb][j] * scale_log2;
-            if (cap_log2 > 0.f) v = cap_log2 * tanhf(v / cap_log2);
+            if (cap_log2 > 0.f) v = softcap_log2(v, cap_log2);
             if (tk < t_lo || tk >= t_hi) v = -CUDART_INF_F;
             s[nb][j] = v;
             mx[j >> 1] = fmaxf(mx[j >> 1], v);

@@ -11,6 +11,16 @@ namespace attn {
 
 constexpr int PAGE_T = 64;  // keys per cache page
 
+// cap * tanh(s / cap) for a score s in log2 units, as cap - 2 cap / (1 + 2^(2 log2(e) s / cap)): one ex2 and one
+// reciprocal of the special-function unit (each good to two units in the last place of a number near 1, so the
+// capped score is off by ~1e-7 * cap at most); a large s gives cap, a very negative one -cap, no NaN on the way.
+__device__ __forceinline__ float softcap_log2(float s, float cap) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(s * (2.8853900817779268f / cap)));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    return fmaf(-2.0f * cap, r, cap);
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
