@@ -391,8 +391,13 @@ def tovalix_kernels(z: dict, T: int, peaks: dict) -> dict:
         flops = 5 * T * H * dk * dv
         us = timed(lambda: ops.linear_recurrence(mode, q, k if mode == "bonus" else None, g, v, c0, c1, o, state[:, :n_state],
                                                   starts, slots, n_seq, H, dk, dv), flush)
-        note(f"{name}: recurrence ({H} heads of {dk} x {dv})", us, nbytes)
-        out[f"{name}: recurrence ({H} heads of {dk} x {dv})"]["gflops"] = round(flops / us / 1e3, 1)
+        note(f"{name}: recurrence ({H} heads of {dk} x {dv})" + (", token by token" if not decode else ""), us, nbytes)
+        if not decode:
+            us = timed(lambda: ops.linear_recurrence(mode, q, k if mode == "bonus" else None, g, v, c0, c1, o, state[:, :n_state],
+                                                     starts, slots, n_seq, H, dk, dv, block_len=128, max_new=T), flush)
+            note(f"{name}: recurrence ({H} heads of {dk} x {dv}), blocks of 128 tokens (what a prompt runs)", us,
+                 nbytes + 4 * (2 * T * H * dk + 3 * (T // 128) * n_state))
+            out[f"{name}: recurrence ({H} heads of {dk} x {dv}), blocks of 128 tokens (what a prompt runs)"]["gflops"] = round(flops / us / 1e3, 1)
         y = torch.empty(T, H * dv, dtype=bf, device=dev)
         wn = torch.ones(H * dv, dtype=bf, device=dev)
         note(f"{name}: head norm, weight" + (", gate" if mode == "bonus" else ""),

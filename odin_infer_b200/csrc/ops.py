@@ -236,7 +236,8 @@ RECURRENCE_MODES = {"bonus": 0, "gated": 1}
 def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: torch.Tensor, v: torch.Tensor,
                       c0: torch.Tensor, c1: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
                       seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int, n_heads: int, dk: int, dv: int,
-                      shift_src: torch.Tensor | None = None, shift_state: torch.Tensor | None = None) -> None:
+                      shift_src: torch.Tensor | None = None, shift_state: torch.Tensor | None = None,
+                      block_len: int = 0, max_new: int = 0) -> None:
     """The recurrence over a matrix-valued state per (sequence, head), S: [dk, dv] in `state`
     (float32 [slots, >= H dk dv], any row stride), sequence b's rows being seq_start[b] .. seq_start[b+1]:
 
@@ -245,7 +246,12 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
 
     q, k, g: float32 [T, H dk] (strided views are fine), v, out: float32 [T, H dv].
     shift_src / shift_state: after the walk the last row of shift_src of every sequence is stored
-    (as float32) in its slot's row of shift_state."""
+    (as float32) in its slot's row of shift_state.
+
+    block_len > 0 (with max_new, the most rows any sequence brings): every sequence's rows are cut into blocks
+    of block_len tokens that are walked side by side from a state of zeros; two small kernels then carry the
+    state from block to block and add each block's incoming state to its tokens' outputs.  The same values up
+    to rounding (sums in another order); for long prompts, which one walk per head cannot fill the GPU with."""
     for t in (q, g, v, out) + ((k,) if k is not None else ()):
         assert t.dtype == torch.float32 and t.stride(1) == 1
     assert state.dtype == torch.float32 and state.stride(1) == 1 and c0.dtype == c1.dtype
@@ -255,14 +261,23 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
     if shift_src is not None:
         assert shift_state is not None and shift_src.is_contiguous() and shift_state.dtype == torch.float32
         width = shift_src.shape[1]
+    n_blocks, qp, s_loc, d_tot, kernels = 0, None, None, None, 1
+    if block_len > 0:
+        assert max_new > 0
+        n_blocks = (max_new + block_len - 1) // block_len
+        T = q.shape[0]
+        qp = torch.empty(T, n_heads * dk, dtype=torch.float32, device=q.device)
+        s_loc = torch.empty(n_seqs * n_blocks, n_heads * dk * dv, dtype=torch.float32, device=q.device)
+        d_tot = torch.empty(n_seqs * n_blocks, n_heads * dk, dtype=torch.float32, device=q.device)
+        kernels = 3
     _check(_fn("recurrent", "odin_linear_recurrence")(
         c_int(RECURRENCE_MODES[mode]), _ptr(q), c_longlong(q.stride(0)), _ptr(kk), c_longlong(kk.stride(0)),
         _ptr(g), c_longlong(g.stride(0)), _ptr(v), c_longlong(v.stride(0)), _ptr(c0), _ptr(c1),
         c_int(dtype_code(c0.dtype)), _ptr(out), c_longlong(out.stride(0)), _ptr(state), c_longlong(state.stride(0)),
         _ptr(seq_start), _ptr(seq_slots), c_int(n_seqs), c_int(n_heads), c_int(dk), c_int(dv), _ptr(shift_src),
         c_int(dtype_code(shift_src.dtype) if shift_src is not None else 0), _ptr(shift_state),
-        c_longlong(shift_state.stride(0) if shift_state is not None else 0), c_int(width), _stream()),
-        "linear_recurrence")
+        c_longlong(shift_state.stride(0) if shift_state is not None else 0), c_int(width), c_int(block_len),
+        c_int(n_blocks), _ptr(qp), _ptr(s_loc), _ptr(d_tot), _stream()), "linear_recurrence", kernels=kernels)
 
 
 def head_unit_scale(o: torch.Tensor, weight: torch.Tensor, per_head_weight: bool, gate: torch.Tensor | None,

@@ -94,6 +94,14 @@ struct RecParams {
     int H, dk, dv;
     // the token shift's memory: after the step the sequence's last row of h goes to its state
     const void* shift_src; int shift_is_bf16; float* shift_state; long long shift_stride; int width;
+    // Blocks of tokens (block_len > 0): a CTA walks one block of one sequence from a state of zeros and leaves
+    // the block's own state in s_loc, the product of the block's decays per key channel in d_tot, and per token
+    // q times the decays since the block's start in qp; two small kernels then carry the state from block to block
+    // and add what each block's incoming state contributes to its tokens' outputs.
+    int block_len, n_blocks;
+    float* qp;     // [rows, H*dk]
+    float* s_loc;  // [sequences * n_blocks][H][dk][dv]
+    float* d_tot;  // [sequences * n_blocks][H*dk]
 };
 
 // One CTA per (sequence, head) walks the sequence's tokens in order.  Column j of S belongs to REC_SPLIT lanes of
@@ -109,7 +117,7 @@ struct RecParams {
 // arithmetic does not depend on which CTA holds it.
 #define REC_COLS 128
 #define REC_FETCH 4   // elements of each input that a thread fetches ahead per block of tokens
-template <int SL, int MODE>
+template <int SL, int MODE, bool BLOCKS>
 __global__ void __launch_bounds__(REC_COLS * REC_SPLIT)
 linear_recurrence_kernel(RecParams p) {
     constexpr int NK = SL * REC_SPLIT;             // key channels the registers hold (dk <= NK)
@@ -118,12 +126,14 @@ linear_recurrence_kernel(RecParams p) {
     __shared__ __align__(16) float sq[TOK][NK], sk[TOK][NK], sw[TOK][NK];
     __shared__ float sv[TOK][REC_COLS], sb[NK];
     pdl_trigger();
-    const int b = blockIdx.x, head = blockIdx.y;
+    const int b = BLOCKS ? blockIdx.x / p.n_blocks : blockIdx.x, head = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int ccols = blockDim.x / REC_SPLIT;      // columns of this CTA
     const int part = lane >> 3, cj = warp * 8 + (lane & 7), j = blockIdx.z * ccols + cj;
     const int dk = p.dk;
-    const int row0 = p.seq_start[b], row1 = p.seq_start[b + 1];
+    const int seq_end = p.seq_start[b + 1];
+    const int row0 = p.seq_start[b] + (BLOCKS ? (int)(blockIdx.x % p.n_blocks) * p.block_len : 0);
+    const int row1 = BLOCKS ? min(seq_end, row0 + p.block_len) : seq_end;
     const int slot = p.seq_slots[b];
     const int hc = head * dk;
     const int tok = max(1, min(TOK, REC_FETCH * (int)blockDim.x / NK));   // tokens per block: what the threads can fetch ahead
@@ -132,10 +142,16 @@ linear_recurrence_kernel(RecParams p) {
     if (row1 <= row0) return;  // an empty (padding) sequence owns no state
     const bool owns = j < p.dv;
     const int i0 = part * SL;
-    float S[SL], ub[BONUS_IN_REGS ? SL : 1];
-    float* st = p.state + (size_t)slot * p.state_stride + (size_t)head * dk * p.dv + j;
+    float S[SL], ub[BONUS_IN_REGS ? SL : 1], D[BLOCKS ? SL : 1];
+    float* st = BLOCKS ? p.s_loc + ((size_t)blockIdx.x * p.H + head) * dk * p.dv + j
+                       : p.state + (size_t)slot * p.state_stride + (size_t)head * dk * p.dv + j;
 #pragma unroll
-    for (int i = 0; i < SL; ++i) S[i] = (owns && i0 + i < dk) ? st[(size_t)(i0 + i) * p.dv] : 0.f;
+    for (int i = 0; i < SL; ++i) S[i] = (!BLOCKS && owns && i0 + i < dk) ? st[(size_t)(i0 + i) * p.dv] : 0.f;
+    if (BLOCKS) {
+#pragma unroll
+        for (int i = 0; i < SL; ++i) D[i] = 1.0f;
+    }
+    const bool writes_qp = BLOCKS && cj == 0 && blockIdx.z == 0;   // one column's lanes write what is per key channel
     __syncthreads();
     if (BONUS_IN_REGS) {
 #pragma unroll
@@ -209,6 +225,14 @@ linear_recurrence_kernel(RecParams p) {
                 for (int e = 0; e < 4; ++e) {
                     const int i = i4 + e;
                     const float kv = kk[e] * vj;
+                    if (BLOCKS) {
+                        // q times the decays between the block's start and this token's look at the state:
+                        // before its own decay where the output comes before the update, after it else
+                        if (MODE == REC_GATED) D[BLOCKS ? i : 0] *= ww[e];
+                        if (writes_qp && i0 + i < dk)
+                            p.qp[(size_t)(t0 + u) * p.H * dk + hc + i0 + i] = qq[e] * D[BLOCKS ? i : 0];
+                        if (MODE == REC_BONUS) D[BLOCKS ? i : 0] *= ww[e];
+                    }
                     if (MODE == REC_BONUS) {
                         const float bonus = BONUS_IN_REGS ? ub[BONUS_IN_REGS ? i : 0] : sb[i0 + i];
                         const float term = qq[e] * fmaf(bonus, kv, S[i]);
@@ -229,11 +253,79 @@ linear_recurrence_kernel(RecParams p) {
 #pragma unroll
     for (int i = 0; i < SL; ++i)
         if (owns && i0 + i < dk) st[(size_t)(i0 + i) * p.dv] = S[i];
-    if (head == 0 && blockIdx.z == 0 && p.shift_src != nullptr) {
+    if (writes_qp) {
+#pragma unroll
+        for (int i = 0; i < SL; ++i)
+            if (i0 + i < dk) p.d_tot[(size_t)blockIdx.x * p.H * dk + hc + i0 + i] = D[BLOCKS ? i : 0];
+    }
+    if (head == 0 && blockIdx.z == 0 && p.shift_src != nullptr && row1 == seq_end) {
         float* dst = p.shift_state + (size_t)slot * p.shift_stride;
         const size_t last = (size_t)(row1 - 1) * p.width;
         for (int c = threadIdx.x; c < p.width; c += blockDim.x)
             dst[c] = p.shift_is_bf16 ? __bfloat162float(((const bf16*)p.shift_src)[last + c]) : ((const float*)p.shift_src)[last + c];
+    }
+}
+
+// The state from block to block: S_in(first block) = the sequence's state; S_in(next) = diag(d_tot) S_in + s_loc.
+// s_loc is overwritten with S_in (what the block's tokens look at); the last S becomes the sequence's state.
+__global__ void __launch_bounds__(256)
+recurrence_carry_kernel(RecParams p) {
+    pdl_trigger();
+    const int b = blockIdx.x, head = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;   // element of the head's state
+    const int row0 = p.seq_start[b], row1 = p.seq_start[b + 1];
+    const int slot = p.seq_slots[b];
+    pdl_wait();
+    if (row1 <= row0 || e >= p.dk * p.dv) return;
+    const int i = e / p.dv;
+    float* st = p.state + (size_t)slot * p.state_stride + (size_t)head * p.dk * p.dv + e;
+    float S = *st;
+    const int n = (row1 - row0 + p.block_len - 1) / p.block_len;
+    for (int c = 0; c < n; ++c) {
+        const size_t item = (size_t)b * p.n_blocks + c;
+        float* loc = p.s_loc + (item * p.H + head) * p.dk * p.dv + e;
+        const float own = *loc;
+        *loc = S;
+        S = fmaf(p.d_tot[item * p.H * p.dk + head * p.dk + i], S, own);
+    }
+    *st = S;
+}
+
+// o[t, head, :] += (q_t * decays since the block's start)^T S_in(block): eight tokens by 32 columns per CTA pass,
+// the incoming state's 32 columns in shared memory.
+__global__ void __launch_bounds__(256)
+recurrence_carry_out_kernel(RecParams p) {
+    __shared__ float tile[REC_MAX_DK][32];
+    pdl_trigger();
+    const int item = blockIdx.x, head = blockIdx.y;
+    const int b = item / p.n_blocks;
+    const int col = blockIdx.z * 32 + (threadIdx.x & 31), lane_t = threadIdx.x >> 5;
+    const int seq_end = p.seq_start[b + 1];
+    const int row0 = p.seq_start[b] + (item % p.n_blocks) * p.block_len;
+    const int row1 = min(seq_end, row0 + p.block_len);
+    pdl_wait();
+    if (row1 <= row0) return;
+    const float* sin = p.s_loc + ((size_t)item * p.H + head) * p.dk * p.dv;
+    for (int e = threadIdx.x; e < p.dk * 32; e += blockDim.x) {
+        const int i = e >> 5, c = blockIdx.z * 32 + (e & 31);
+        tile[i][e & 31] = c < p.dv ? sin[(size_t)i * p.dv + c] : 0.f;
+    }
+    __syncthreads();
+    const size_t qs = (size_t)p.H * p.dk;
+    for (int t0 = row0 + lane_t * 4; t0 < row1; t0 += 32) {   // a warp takes four tokens at a time
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* qrow = p.qp + (size_t)t0 * qs + (size_t)head * p.dk;
+        for (int i = 0; i < p.dk; ++i) {
+            const float sv = tile[i][threadIdx.x & 31];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (t0 + u < row1) acc[u] = fmaf(__ldg(qrow + u * qs + i), sv, acc[u]);
+        }
+        if (col < p.dv) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (t0 + u < row1) p.o[(size_t)(t0 + u) * p.o_stride + (size_t)head * p.dv + col] += acc[u];
+        }
     }
 }
 
@@ -242,8 +334,12 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
                                       const void* c0, const void* c1, int c_dtype, float* o, long long o_stride,
                                       float* state, long long state_stride, const int* seq_start, const int* seq_slots,
                                       int n_seqs, int H, int dk, int dv, const void* shift_src, int shift_dtype,
-                                      float* shift_state, long long shift_stride, int width, void* stream) {
+                                      float* shift_state, long long shift_stride, int width, int block_len, int n_blocks,
+                                      float* qp, float* s_loc, float* d_tot, void* stream) {
     if (n_seqs <= 0) return 0;
+    if (block_len < 0 || (block_len > 0 && (n_blocks <= 0 || qp == nullptr || s_loc == nullptr || d_tot == nullptr ||
+                                            (long long)n_seqs * n_blocks > 2147483647LL)))
+        return ODIN_ERR_BAD_ARG;
     if (H <= 0 || dk <= 0 || dk > REC_MAX_DK || dv <= 0 || dv > 256 || H > 65535) return ODIN_ERR_UNSUPPORTED;
     if (mode != REC_BONUS && mode != REC_GATED) return ODIN_ERR_BAD_ARG;
     RecParams p;
@@ -254,18 +350,23 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
     p.seq_start = seq_start; p.seq_slots = seq_slots; p.H = H; p.dk = dk; p.dv = dv;
     p.shift_src = shift_src; p.shift_is_bf16 = shift_dtype == ODIN_BF16; p.shift_state = shift_state;
     p.shift_stride = shift_stride; p.width = width;
+    p.block_len = block_len; p.n_blocks = n_blocks; p.qp = qp; p.s_loc = s_loc; p.d_tot = d_tot;
+    const bool blocks = block_len > 0;
+    const int n_items = blocks ? n_seqs * n_blocks : n_seqs;
     cudaStream_t s = (cudaStream_t)stream;
     // columns per CTA: all of them (up to REC_COLS) when (sequence, head) pairs alone fill the GPU twice, else
     // halved down to 32 until they do
     int cols = (dv < REC_COLS ? dv : REC_COLS);
     cols = (cols + 7) / 8 * 8;
-    while (cols > 32 && (cols / 2) % 8 == 0 && (long long)n_seqs * H * ((dv + cols - 1) / cols) < 2 * 148) cols /= 2;
+    while (cols > 32 && (cols / 2) % 8 == 0 && (long long)n_items * H * ((dv + cols - 1) / cols) < 2 * 148) cols /= 2;
     const int threads = cols * REC_SPLIT;      // a warp per eight columns
-    dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
+    dim3 grid(n_items, H, (dv + cols - 1) / cols);
 #define GO(SL)                                                                                                  \
     do {                                                                                                        \
-        if (mode == REC_BONUS) odin_launch(linear_recurrence_kernel<SL, REC_BONUS>, grid, dim3(threads), 0, s, p);  \
-        else odin_launch(linear_recurrence_kernel<SL, REC_GATED>, grid, dim3(threads), 0, s, p);                \
+        if (mode == REC_BONUS && blocks) odin_launch(linear_recurrence_kernel<SL, REC_BONUS, true>, grid, dim3(threads), 0, s, p);  \
+        else if (mode == REC_BONUS) odin_launch(linear_recurrence_kernel<SL, REC_BONUS, false>, grid, dim3(threads), 0, s, p);     \
+        else if (blocks) odin_launch(linear_recurrence_kernel<SL, REC_GATED, true>, grid, dim3(threads), 0, s, p);  \
+        else odin_launch(linear_recurrence_kernel<SL, REC_GATED, false>, grid, dim3(threads), 0, s, p);         \
     } while (0)
     // registers for the smallest multiple of REC_SPLIT channels that holds dk
     if (dk <= 16) GO(4);
@@ -277,6 +378,12 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
     else GO(64);
 #undef GO
     ODIN_LAUNCH_CHECK();
+    if (blocks) {
+        odin_launch(recurrence_carry_kernel, dim3(n_seqs, H, (dk * dv + 255) / 256), dim3(256), 0, s, p);
+        ODIN_LAUNCH_CHECK();
+        odin_launch(recurrence_carry_out_kernel, dim3(n_items, H, (dv + 31) / 32), dim3(256), 0, s, p);
+        ODIN_LAUNCH_CHECK();
+    }
     return 0;
 }
 

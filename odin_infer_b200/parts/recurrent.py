@@ -13,6 +13,16 @@ from ..csrc import ops
 from .base import Mixer, ParamSpec, register_part
 
 
+# A step in which a sequence brings this many tokens or more walks the recurrence in blocks of RECURRENCE_BLOCK
+# tokens side by side (see ops.linear_recurrence); shorter steps, and every decode step, walk token by token.
+RECURRENCE_BLOCK = 128
+BLOCKS_FROM = 2 * RECURRENCE_BLOCK
+
+
+def _block_len(step) -> int:
+    return RECURRENCE_BLOCK if step.max_new >= BLOCKS_FROM else 0
+
+
 def _f32_view(state_bytes: torch.Tensor) -> torch.Tensor:
     """The state rows (uint8 [slots, bytes], rows any distance apart) as float32 [slots, bytes / 4]."""
     return state_bytes.view(torch.float32)
@@ -86,7 +96,8 @@ class TokenShiftWKV(Mixer):
         raw = rt.linear(bent, self.w["w2"], out_dtype=torch.float32)
         o = rt.empty(T, inner, dtype=torch.float32)
         ops.linear_recurrence("bonus", r, k, raw, v, self.w0, self.u, o, S, step.seq_start, step.seq_slots,
-                              step.n_seq_cap, self.H, self.D, self.D, shift_src=h, shift_state=before)
+                              step.n_seq_cap, self.H, self.D, self.D, shift_src=h, shift_state=before,
+                              block_len=_block_len(step), max_new=step.max_new)
         y = rt.empty(T, inner)
         ops.head_unit_scale(o, self.w["norm"], True, g, self.eps, y, self.H, self.D)
         return rt.linear(y, self.w["o"], out_dtype=torch.float32, may_split=True, add_to=residual)
@@ -143,7 +154,7 @@ class GatedLinearRecurrence(Mixer):
         o = rt.empty(T, vv, dtype=torch.float32)
         ops.linear_recurrence("gated", qfv[:, :qk], None, qfv[:, qk:2 * qk], qfv[:, 2 * qk:], self.f_bias, self.lower, o,
                               _f32_view(step.state(entry)), step.seq_start, step.seq_slots, step.n_seq_cap,
-                              self.H, self.D, self.V)
+                              self.H, self.D, self.V, block_len=_block_len(step), max_new=step.max_new)
         y = rt.empty(T, vv)
         ops.head_unit_scale(o, self.norm_w, False, None, self.eps, y, self.H, self.V)
         return rt.linear(y, self.w_o, out_dtype=torch.float32, may_split=True, add_to=residual)

@@ -348,6 +348,36 @@ def test_linear_recurrence_alone(mode, H, dk, dv):
     assert float(state[0].abs().max()) == 0 and float(state[:, n_state:].abs().max()) == 0   # the empty sequence's slot, the neighbours' bytes
 
 
+@pytest.mark.parametrize("mode", ["bonus", "gated"])
+@pytest.mark.parametrize("H,dk,dv,block", [(2, 64, 64, 32), (3, 16, 24, 7), (1, 128, 40, 64), (2, 40, 72, 16)])
+def test_linear_recurrence_in_blocks_of_tokens(mode, H, dk, dv, block):
+    """The same recurrence with every sequence cut into blocks that are walked side by side: sequences of 150, 0, 1 and
+    block + 1 tokens that go on from a state which is not zero, against the walk token by token in float64."""
+    from odin_infer_b200.csrc import ops
+    lens = [150, 0, 1, block + 1]
+    T = sum(lens)
+    q, k, g, v, c0, c1 = _recurrence_inputs(T, H, dk, dv, seed=3 * dk + dv)
+    n_state = H * dk * dv
+    state = torch.randn(6, n_state + 8, device=DEV)
+    slots = torch.tensor([4, 0, 2, 5], dtype=torch.int32, device=DEV)
+    starts = torch.tensor([0, 150, 150, 151, T], dtype=torch.int32, device=DEV)
+    before = state.clone()
+    dev = [t.to(DEV) for t in (q, k, g, v, c0, c1)]
+    out = torch.empty(T, H * dv, device=DEV)
+    ops.linear_recurrence(mode, dev[0], dev[1] if mode == "bonus" else None, dev[2], dev[3], dev[4], dev[5], out,
+                          state[:, :n_state], starts, slots, 4, H, dk, dv, block_len=block, max_new=150)
+    at = 0
+    for slot, n in zip(slots.tolist(), lens):
+        if n == 0:
+            continue
+        S = before[slot, :n_state].double().cpu().reshape(H, dk, dv).clone()
+        ref = plain_recurrence(mode, q[at:at + n], k[at:at + n], g[at:at + n], v[at:at + n], c0, c1, H, dk, dv, S)
+        close(out[at:at + n], ref, 2e-5)
+        close(state[slot, :n_state], S.reshape(-1), 2e-5)
+        at += n
+    assert torch.equal(state[0], before[0]) and torch.equal(state[:, n_state:], before[:, n_state:])
+
+
 def test_token_shift_alone():
     from odin_infer_b200.csrc import ops
     torch.manual_seed(3)
