@@ -320,7 +320,7 @@ def plain_recurrence(mode, q, k, g, v, c0, c1, H, dk, dv, S):
 
 
 @pytest.mark.parametrize("mode", ["bonus", "gated"])
-@pytest.mark.parametrize("H,dk,dv", [(3, 16, 16), (2, 64, 64), (1, 20, 12), (2, 40, 72), (2, 128, 32)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 16, 16), (2, 64, 64), (1, 20, 12), (2, 40, 72), (2, 128, 32), (1, 160, 136), (1, 256, 8)])
 def test_linear_recurrence_alone(mode, H, dk, dv):
     """Two sequences of unequal length and an empty one in one launch, then a second launch that goes on from the
     state; state rows far apart (another mixer's bytes between them); register kernels and the general one."""
@@ -349,7 +349,7 @@ def test_linear_recurrence_alone(mode, H, dk, dv):
 
 
 @pytest.mark.parametrize("mode", ["bonus", "gated"])
-@pytest.mark.parametrize("H,dk,dv,block", [(2, 64, 64, 32), (3, 16, 24, 7), (1, 128, 40, 64), (2, 40, 72, 16)])
+@pytest.mark.parametrize("H,dk,dv,block", [(2, 64, 64, 32), (3, 16, 24, 7), (1, 128, 40, 64), (2, 40, 72, 16), (1, 200, 256, 50)])
 def test_linear_recurrence_in_blocks_of_tokens(mode, H, dk, dv, block):
     """The same recurrence with every sequence cut into blocks that are walked side by side: sequences of 150, 0, 1 and
     block + 1 tokens that go on from a state which is not zero, against the walk token by token in float64."""
