@@ -359,6 +359,9 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
     int cols = (dv < REC_COLS ? dv : REC_COLS);
     cols = (cols + 7) / 8 * 8;
     while (cols > 32 && (cols / 2) % 8 == 0 && (long long)n_items * H * ((dv + cols - 1) / cols) < 2 * 148) cols /= 2;
+    // a block of tokens is staged by the CTA's threads, REC_FETCH elements each: enough threads for one token's channels
+    const int sl = dk <= 16 ? 4 : dk <= 32 ? 8 : dk <= 48 ? 12 : dk <= 64 ? 16 : dk <= 96 ? 24 : dk <= 128 ? 32 : 64;
+    if (cols * REC_SPLIT * REC_FETCH < sl * REC_SPLIT) cols = (sl / REC_FETCH + 7) / 8 * 8;
     const int threads = cols * REC_SPLIT;      // a warp per eight columns
     dim3 grid(n_items, H, (dv + cols - 1) / cols);
 #define GO(SL)                                                                                                  \
