@@ -240,6 +240,58 @@ def test_the_command_line_generates(folders, capsys):
     assert out and len(out[0]["tokens"]) == 5
 
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn at random: order and number of layers, every size, every constant."""
+    rng = np.random.default_rng(seed)
+    pick = lambda xs: xs[int(rng.integers(len(xs)))]   # noqa: E731
+    groups = pick([1, 2, 3, 4])
+    width = groups * pick([8, 12, 20, 24, 32]) * pick([1, 2])
+    layers, writers = [], []
+    for i in range(int(rng.integers(3, 7))):
+        kind = pick(["attention", "attention", "wkv", "hgrn2"])
+        ff = pick([0, 40, 72, 128])
+        if kind == "attention":
+            if writers and rng.random() < 0.5:
+                src = pick(writers)
+                m = json.loads(json.dumps(layers[src]["mixer"]))
+                m.update(kv_from=src, scale=float(rng.uniform(0.05, 0.4)), mask={"size": int(rng.integers(3, 260))})
+                m["heads"] = m["kv_heads"] * pick([1, 2, 3])
+                if rng.random() < 0.5:
+                    m["softcap"] = float(rng.uniform(3, 40))
+            else:
+                dim = pick([16, 24, 40, 64, 64, 96, 128])
+                kv = pick([1, 2, 3])
+                m = att(kv * pick([1, 2, 4]), kv, dim, pick([dim, dim, 8, 48]), pick([dim, dim, dim // 2, 2 * (dim // 8)]),
+                        float(pick([1e3, 1e4, 5e5])), int(rng.integers(3, 260)), float(rng.uniform(0.05, 0.4)),
+                        float(rng.uniform(3, 40)) if rng.random() < 0.8 else None)
+                writers.append(i)
+        elif kind == "wkv":
+            m = {"heads": pick([1, 2, 5]), "dim": pick([8, 16, 24, 64]), "decay_rank": pick([4, 8, 24])}
+        else:
+            m = {"heads": pick([1, 3, 4]), "dim": pick([8, 20, 32, 64]), "vdim": pick([8, 12, 32, 64])}
+        layers.append(layer(kind, m, ff))
+    cfg = {"architecture": "Tovalix", "vocab": int(rng.integers(40, 400)), "width": width,
+           "norm": {"eps": float(pick([1e-5, 1e-6])), "groups": groups}, "layers": layers}
+    if rng.random() < 0.7:
+        cfg["token_side"] = {"dim": pick([3, 8, 16])}
+    return cfg
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [101, 102, 103, 104, 105, 106, 107, 108])
+def test_configurations_drawn_at_random(tmp_path, seed, dtype):
+    """Whole prompts, the last tokens one by one, and an unequal batch, for configurations that nobody chose."""
+    from odin_infer_b200.config import config_from_dict
+    from odin_infer_b200.weights import write_random_model
+    raw = random_config(seed)
+    folder = write_random_model(os.path.join(str(tmp_path), "m"), config_from_dict(raw), seed)
+    reqs = requests_for(raw, [1, 47, 290], seed=seed)
+    engine = engine_for(folder, dtype)
+    for recs in (traces.whole(reqs), traces.tail_one_by_one(reqs, tail=33), traces.batches(reqs, 3, first_part=lambda n: max(1, n - 20))):
+        check_rows(traces.collect(recs, replay(engine, recs)), folder, reqs, dtype)
+    engine.destroy()
+
+
 # --------------------------------------------------------------------------------------
 # every mechanism alone, with inputs that show a fault
 # --------------------------------------------------------------------------------------
