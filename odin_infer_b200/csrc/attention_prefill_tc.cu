@@ -103,7 +103,9 @@ __device__ unsigned long long* odin_attn_clk = nullptr;
 // The persistent CTAs' work counter and the count of CTAs that have left (see the kernel).
 __device__ unsigned int g_prefill_next = 0, g_prefill_done = 0;
 
-template <int HD>
+// EXTRA: the kernel knows a chunk mask and capped scores; without them it is compiled as it was before they
+// existed (the softmax threads' loop is sensitive to every register and instruction).
+template <int HD, bool EXTRA>
 __global__ void __launch_bounds__(320, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const PrefillTcParams p) {
@@ -191,7 +193,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     int first_key = 0;
     if (p.window > 0 && pos0 - p.window + 1 > 0) first_key = pos0 - p.window + 1;
-    if (p.chunk > 0) first_key = max(first_key, (pos0 / p.chunk) * p.chunk);  // the tile's first row sees furthest back
+    if (EXTRA && p.chunk > 0) first_key = max(first_key, (pos0 / p.chunk) * p.chunk);  // the tile's first row sees furthest back
     const int page_a = first_key / PAGE_T, page_b = (pos0 + rows - 1) / PAGE_T;  // inclusive
     const int n_pages = page_b - page_a + 1;
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
@@ -320,9 +322,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const int pos = pos0 + row;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         // capped scores are brought to log2 units as they are capped; nothing is left to scale then
-        const float scale = p.cap_log2 > 0.f ? 1.0f : p.scale_log2;
-        const float cap = p.cap_log2, cap_in = p.cap_log2 > 0.f ? 2.0f * 1.4426950408889634f * p.scale_log2 / p.cap_log2 : 0.f;
-        const int chunk_lo = p.chunk > 0 ? (pos / p.chunk) * p.chunk : 0;
+        const float scale = (EXTRA && p.cap_log2 > 0.f) ? 1.0f : p.scale_log2;
+        const float cap = EXTRA ? p.cap_log2 : 0.f;
+        const float cap_in = (EXTRA && p.cap_log2 > 0.f) ? 2.0f * 1.4426950408889634f * p.scale_log2 / p.cap_log2 : 0.f;
+        const int chunk_lo = (EXTRA && p.chunk > 0) ? (pos / p.chunk) * p.chunk : 0;
         float m_run = -CUDART_INF_F;   // the maximum that the sums and O are scaled by (in log2 units)
         float l_run = 0.f;             // this thread's share of the row's sum
         bool ok = true;
@@ -336,7 +339,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             tc::tmem_ld_wait();
             CLK(1, 21);  // read
             const int key0 = pg * PAGE_T + half * 32;
-            if (cap > 0.f) {
+            if (EXTRA && cap > 0.f) {
                 // cap * tanh(s / cap) with tanh(x) = 1 - 2 / (1 + e^(2x)): one ex2 and one reciprocal
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
@@ -346,11 +349,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     sr[c] = __float_as_uint(fmaf(-2.0f * cap, r, cap));
                 }
             }
-            if ((pg * PAGE_T + PAGE_T - 1 > pos0) || p.window > 0 || p.chunk > 0) {  // a page on the diagonal or at a mask's edge
+            if ((pg * PAGE_T + PAGE_T - 1 > pos0) || p.window > 0 || (EXTRA && p.chunk > 0)) {  // a page on the diagonal or at a mask's edge
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const int t = key0 + c;
-                    if (t > pos || (p.window > 0 && t <= pos - p.window) || t < chunk_lo) sr[c] = 0xff800000u;  // -inf
+                    if (t > pos || (p.window > 0 && t <= pos - p.window) || (EXTRA && t < chunk_lo)) sr[c] = 0xff800000u;  // -inf
                 }
             }
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
@@ -482,14 +485,14 @@ int* tc_error_flag() {
     return flag;
 }
 
-template <int HD>
+template <int HD, bool EXTRA>
 int launch_prefill_tc(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcParams& p, int n_seqs, int max_new,
                       cudaStream_t s) {
     // tiles + barriers + slack for the 1 KB alignment; two CTAs of head size 128 just fit an SM's 228 KB
     constexpr int SMEM = (HD / 64) * BQT * 128 + 4 * PAGE_T * HD * 2 + 128 + 2048 + 896;  // (barriers 128, exchange 2048, alignment 896)
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -502,7 +505,7 @@ int launch_prefill_tc(const CUtensorMap& mk, const CUtensorMap& mv, const Prefil
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
     const int grid = (int)(total < 2LL * sms ? total : 2LL * sms);
-    odin_launch(attn_prefill_tc_kernel<HD>, dim3(grid), dim3(320), (size_t)SMEM, s, mk, mv, q);
+    odin_launch(attn_prefill_tc_kernel<HD, EXTRA>, dim3(grid), dim3(320), (size_t)SMEM, s, mk, mv, q);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
@@ -537,8 +540,9 @@ extern "C" int odin_attention_prefill_tc_masked(const void* q, long long q_row_s
     p.cap_log2 = softcap > 0.f ? 1.4426950408889634f * softcap : 0.f;
     p.error = tc_error_flag();
     cudaStream_t s = (cudaStream_t)stream;
-    if (hd == 64) return launch_prefill_tc<64>(mk, mv, p, n_seqs, max_new, s);
-    if (hd == 128) return launch_prefill_tc<128>(mk, mv, p, n_seqs, max_new, s);
+    const bool extra = chunk > 0 || softcap > 0.f;
+    if (hd == 64) return extra ? launch_prefill_tc<64, true>(mk, mv, p, n_seqs, max_new, s) : launch_prefill_tc<64, false>(mk, mv, p, n_seqs, max_new, s);
+    if (hd == 128) return extra ? launch_prefill_tc<128, true>(mk, mv, p, n_seqs, max_new, s) : launch_prefill_tc<128, false>(mk, mv, p, n_seqs, max_new, s);
     return ODIN_ERR_UNSUPPORTED;
 }
 
