@@ -12,7 +12,8 @@
 // keys before the query's own chunk (position p sees t only if t / chunk == p / chunk, chunks
 // counted from the sequence's first position).  scale > 0 replaces 1 / sqrt(hd); softcap > 0
 // turns a score s into softcap * tanh(s / softcap) before the softmax.  A value head has vd
-// elements (keys and queries hd).
+// elements (keys and queries hd).  sink (optional, one 32-bit number per query head): exp(sink[h]) is
+// added to the softmax's denominator once.
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -67,7 +68,7 @@ attention_plain_kernel(const T* __restrict__ q, size_t q_stride, T* __restrict__
                        int Hq, int Hkv, int hd, int vd, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                        int page_size, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                        const int* __restrict__ block_table, int bt_stride, int window, int chunk, float scale,
-                       float softcap) {
+                       float softcap, const float* __restrict__ sink) {
     __shared__ float qs[AP_WARPS][AP_MAX_HD];
     pdl_trigger();
     pdl_wait();
@@ -130,6 +131,15 @@ attention_plain_kernel(const T* __restrict__ q, size_t q_stride, T* __restrict__
             }
         }
     }
+    if (sink != nullptr) {
+        // a learned logit per query head that enters the denominator alone: no key, no value, not scaled
+        const float sk = sink[h];
+        const float m_new = fmaxf(m, sk);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int r = 0; r < AP_MAX_HD / 32; ++r) acc[r] *= corr;
+    }
     T* orow = out + (size_t)t * out_stride + (size_t)h * vd;
     const float inv_l = (l > 0.f) ? 1.0f / l : 0.f;
 #pragma unroll
@@ -144,7 +154,7 @@ extern "C" int odin_attention_plain(const void* q, long long q_row_stride, void*
                                     int dtype, int T, int Hq, int Hkv, int hd, int vd, const void* k_cache,
                                     const void* v_cache, int page_size, const int* tok_pos, const int* tok_seq,
                                     const int* block_table, int bt_stride, int window, int chunk, float scale,
-                                    float softcap, void* stream) {
+                                    float softcap, const float* sink, void* stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > AP_MAX_HD || vd <= 0 || vd > AP_MAX_HD || Hkv <= 0 || Hq % Hkv != 0 ||
         window < 0 || chunk < 0)
@@ -157,12 +167,12 @@ extern "C" int odin_attention_plain(const void* q, long long q_row_stride, void*
         odin_launch(attention_plain_kernel<bf16>, dim3((unsigned)blocks), dim3(AP_WARPS * 32), 0, s,
             (const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, T, Hq, Hkv, hd, vd,
             (const bf16*)k_cache, (const bf16*)v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride, window,
-            chunk, scale, softcap);
+            chunk, scale, softcap, sink);
     else if (dtype == ODIN_F32)
         odin_launch(attention_plain_kernel<float>, dim3((unsigned)blocks), dim3(AP_WARPS * 32), 0, s,
             (const float*)q, (size_t)q_row_stride, (float*)out, (size_t)out_row_stride, T, Hq, Hkv, hd, vd,
             (const float*)k_cache, (const float*)v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride,
-            window, chunk, scale, softcap);
+            window, chunk, scale, softcap, sink);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();

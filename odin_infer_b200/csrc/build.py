@@ -29,6 +29,7 @@ GROUPS = {
     "elementwise": ["elementwise.cu"],
     "rowwise": ["rowwise.cu"],
     "recurrent": ["recurrent.cu"],
+    "moe": ["moe.cu"],
     "gemm_plain": ["gemm_plain.cu"],
     "head_prep": ["head_prep.cu"],
     "attention_plain": ["attention_plain.cu"],

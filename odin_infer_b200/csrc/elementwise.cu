@@ -11,7 +11,7 @@
 // ---------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int d, int V) {
+                             float* __restrict__ out, int d, int V, float scale) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -19,18 +19,18 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
     const bool ok = (id >= 0 && id < V);
     const TW* row = table + (size_t)(ok ? id : 0) * d;
     float* o = out + (size_t)t * d;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = ok ? to_f32(row[j]) : 0.f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = ok ? to_f32(row[j]) * scale : 0.f;
 }
 
 extern "C" int odin_embed(const void* table, int table_dtype, const int* ids, float* out,
-                          int T, int d, int V, void* stream) {
+                          int T, int d, int V, float scale, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == ODIN_BF16)
-        odin_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, s, (const bf16*)table, ids, out, d, V);
+        odin_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, s, (const bf16*)table, ids, out, d, V, scale);
     else if (table_dtype == ODIN_F32)
-        odin_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)table, ids, out, d, V);
+        odin_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)table, ids, out, d, V, scale);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();

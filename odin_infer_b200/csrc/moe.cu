@@ -1,0 +1,257 @@
+// Mixture of experts on the CUDA cores: the router, and the experts' two products for the rows
+// (token, choice) with each row reading the weights of its own expert.
+//
+//   router:   z = W_r h + b in 32-bit; the `top` largest logits are chosen (the lower index wins a tie),
+//             their weights are the softmax over the chosen logits alone; `always` further rows per
+//             token name the experts E, E + 1, ... with weight 1 (experts that every token uses).
+//   gate|up:  a[r, j] = act(Wg[e_r] h_t)_j * (Wu[e_r] h_t)_j          r = t * rows_per_token + k
+//   down:     y[k, t, :] = weight_r * Wd[e_r] a[r, :]                 32-bit, one slice per choice
+//
+// The slices y[k] are partial sums of the layer's update: whoever adds the update adds them in the
+// order k = 0, 1, ...  Every sum runs in an order fixed by the sizes alone (a warp per output element,
+// lanes striding the row), so a token's values do not depend on the batch.  These kernels serve the
+// 32-bit path and steps of few tokens; rows of padding (sequence -1) get expert -1 and write zeros.
+#include "common.cuh"
+#include <math_constants.h>
+
+#define MOE_THREADS 256
+#define MOE_WARPS (MOE_THREADS / 32)
+#define MOE_COLS 64  // output columns per block
+
+#define MOE_ACT_SILU 1
+#define MOE_ACT_GELU_TANH 2
+
+__device__ __forceinline__ float moe_activate(int act, float z) {
+    if (act == MOE_ACT_SILU) return z / (1.0f + expf(-z));
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// sum_i w[i] x[i] over a row of n elements: lanes stride the row, the warp adds up; every lane gets the sum
+__device__ __forceinline__ float warp_dot(const float* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float acc = 0.f;
+    if ((n & 3) == 0 && (((uintptr_t)w) & 15) == 0) {
+        for (int i = lane * 4; i < n; i += 128) {
+            const float4 v = *reinterpret_cast<const float4*>(w + i);
+            acc = fmaf(v.x, x[i], acc);
+            acc = fmaf(v.y, x[i + 1], acc);
+            acc = fmaf(v.z, x[i + 2], acc);
+            acc = fmaf(v.w, x[i + 3], acc);
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) acc = fmaf(w[i], x[i], acc);
+    }
+    return warp_sum(acc);
+}
+
+__device__ __forceinline__ float warp_dot(const bf16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
+    float acc = 0.f;
+    if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+        for (int i = lane * 8; i < n; i += 256) {
+            const uint4 v = *reinterpret_cast<const uint4*>(w + i);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(p[j]);
+                acc = fmaf(f.x, x[i + 2 * j], acc);
+                acc = fmaf(f.y, x[i + 2 * j + 1], acc);
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) acc = fmaf(__bfloat162float(w[i]), x[i], acc);
+    }
+    return warp_sum(acc);
+}
+
+// ------------------------------------------------------------ router
+// One block per token.  ids, wts: [T, top + always].
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(128)
+moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restrict__ w, VecRef bias, int E, int d, int top,
+                  int always, const int* __restrict__ tok_seq, int* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float sm[];
+    float* hrow = sm;       // d
+    float* z = sm + d;      // E
+    pdl_trigger();
+    const int t = blockIdx.x, per = top + always;
+    const bool real = tok_seq == nullptr || tok_seq[t] >= 0;
+    pdl_wait();
+    if (!real) {
+        for (int k = threadIdx.x; k < per; k += blockDim.x) {
+            ids[(size_t)t * per + k] = -1;
+            wts[(size_t)t * per + k] = 0.f;
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < d; i += blockDim.x) hrow[i] = to_f32(h[(size_t)t * h_stride + i]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += n_warps) {
+        const float s = warp_dot(w + (size_t)e * d, hrow, d, lane);
+        if (lane == 0) z[e] = s + (bias.p != nullptr ? bias.at(e) : 0.f);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // `top` rounds of a warp-wide arg max; the chosen logit is taken out by -inf
+        float chosen = 0.f, first = 0.f, sum = 0.f;
+        int chosen_id = -1;
+        for (int k = 0; k < top; ++k) {
+            float best = -CUDART_INF_F;
+            int best_e = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = z[e];
+                if (v > best) { best = v; best_e = e; }  // ascending e: the lower index stays on a tie
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+            }
+            if (k == 0) first = best;
+            const float p = expf(best - first);
+            sum += p;
+            if (lane == k) { chosen = p; chosen_id = best_e; }
+            if (lane == 0 && best_e < E) z[best_e] = -CUDART_INF_F;
+            __syncwarp();
+        }
+        if (lane < top) {
+            ids[(size_t)t * per + lane] = chosen_id < E ? chosen_id : -1;
+            wts[(size_t)t * per + lane] = chosen / sum;
+        }
+        for (int k = lane; k < always; k += 32) {
+            ids[(size_t)t * per + top + k] = E + k;
+            wts[(size_t)t * per + top + k] = 1.0f;
+        }
+    }
+}
+
+extern "C" int odin_moe_router(const void* h, int h_dtype, long long h_stride, const void* w, int w_dtype, const void* bias,
+                               int bias_dtype, int T, int E, int d, int top, int always, const int* tok_seq, int* ids,
+                               float* wts, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > 32 || top > E || always < 0 || d <= 0) return ODIN_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(d + E) * sizeof(float);
+    if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    VecRef bv{bias, bias_dtype == ODIN_BF16};
+#define GO(TH, TW)                                                                                                   \
+    do {                                                                                                             \
+        if (smem > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(moe_router_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        odin_launch(moe_router_kernel<TH, TW>, dim3(T), dim3(128), smem, s, (const TH*)h, (size_t)h_stride,          \
+                    (const TW*)w, bv, E, d, top, always, tok_seq, ids, wts);                                         \
+    } while (0)
+    if (h_dtype == ODIN_BF16 && w_dtype == ODIN_BF16) GO(bf16, bf16);
+    else if (h_dtype == ODIN_F32 && w_dtype == ODIN_F32) GO(float, float);
+    else if (h_dtype == ODIN_BF16 && w_dtype == ODIN_F32) GO(bf16, float);
+    else if (h_dtype == ODIN_F32 && w_dtype == ODIN_BF16) GO(float, bf16);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ gate|up of the rows' own experts
+// grid (rows, column blocks).  w: [experts][2 ff][d], the ff gate rows before the ff up rows.
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(MOE_THREADS)
+moe_gate_up_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restrict__ w, const int* __restrict__ ids, int per,
+                   int ff, int d, int act, TH* __restrict__ out) {
+    extern __shared__ float hrow[];  // d
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x, t = r / per;
+    const int e = ids[r];
+    const int c0 = blockIdx.y * MOE_COLS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TH* orow = out + (size_t)r * ff;
+    if (e < 0) {
+        for (int j = c0 + threadIdx.x; j < min(ff, c0 + MOE_COLS); j += blockDim.x) orow[j] = from_f32<TH>(0.f);
+        return;
+    }
+    for (int i = threadIdx.x; i < d; i += blockDim.x) hrow[i] = to_f32(h[(size_t)t * h_stride + i]);
+    __syncthreads();
+    const TW* we = w + (size_t)e * 2 * ff * d;
+    for (int j = c0 + warp; j < min(ff, c0 + MOE_COLS); j += MOE_WARPS) {
+        const float g = warp_dot(we + (size_t)j * d, hrow, d, lane);
+        const float u = warp_dot(we + (size_t)(ff + j) * d, hrow, d, lane);
+        if (lane == 0) orow[j] = from_f32<TH>(moe_activate(act, g) * u);
+    }
+}
+
+extern "C" int odin_moe_gate_up(const void* h, int h_dtype, long long h_stride, const void* w, int w_dtype, const int* ids,
+                                int T, int per, int ff, int d, int act, void* out, void* stream) {
+    if (T <= 0 || per <= 0) return 0;
+    if (act != MOE_ACT_SILU && act != MOE_ACT_GELU_TANH) return ODIN_ERR_BAD_ARG;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 200 * 1024 || (long long)T * per > 2147483647LL) return ODIN_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((unsigned)(T * per), (unsigned)((ff + MOE_COLS - 1) / MOE_COLS));
+#define GO(TH, TW)                                                                                                    \
+    do {                                                                                                              \
+        if (smem > 48 * 1024)                                                                                         \
+            cudaFuncSetAttribute(moe_gate_up_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        odin_launch(moe_gate_up_kernel<TH, TW>, grid, dim3(MOE_THREADS), smem, s, (const TH*)h, (size_t)h_stride,     \
+                    (const TW*)w, ids, per, ff, d, act, (TH*)out);                                                    \
+    } while (0)
+    if (h_dtype == ODIN_BF16 && w_dtype == ODIN_BF16) GO(bf16, bf16);
+    else if (h_dtype == ODIN_F32 && w_dtype == ODIN_F32) GO(float, float);
+    else if (h_dtype == ODIN_BF16 && w_dtype == ODIN_F32) GO(bf16, float);
+    else if (h_dtype == ODIN_F32 && w_dtype == ODIN_BF16) GO(float, bf16);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ down product of the rows' own experts, weighted
+// a: [T * per, ff]; w: [experts][d][ff]; y: [per][T][d] 32-bit, y[k][t] = wts[t, k] * Wd[e] a[t * per + k]
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(MOE_THREADS)
+moe_down_kernel(const TA* __restrict__ a, const TW* __restrict__ w, const int* __restrict__ ids, const float* __restrict__ wts,
+                int T, int per, int ff, int d, float* __restrict__ y) {
+    extern __shared__ float arow[];  // ff
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x, t = r / per, k = r % per;
+    const int e = ids[r];
+    const int c0 = blockIdx.y * MOE_COLS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* yrow = y + ((size_t)k * T + t) * d;
+    if (e < 0) {
+        for (int c = c0 + threadIdx.x; c < min(d, c0 + MOE_COLS); c += blockDim.x) yrow[c] = 0.f;
+        return;
+    }
+    for (int i = threadIdx.x; i < ff; i += blockDim.x) arow[i] = to_f32(a[(size_t)r * ff + i]);
+    __syncthreads();
+    const float wt = wts[r];
+    const TW* we = w + (size_t)e * d * ff;
+    for (int c = c0 + warp; c < min(d, c0 + MOE_COLS); c += MOE_WARPS) {
+        const float s = warp_dot(we + (size_t)c * ff, arow, ff, lane);
+        if (lane == 0) yrow[c] = wt * s;
+    }
+}
+
+extern "C" int odin_moe_down(const void* a, int a_dtype, const void* w, int w_dtype, const int* ids, const float* wts, int T,
+                             int per, int ff, int d, float* y, void* stream) {
+    if (T <= 0 || per <= 0) return 0;
+    const size_t smem = (size_t)ff * sizeof(float);
+    if (smem > 200 * 1024 || (long long)T * per > 2147483647LL) return ODIN_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((unsigned)(T * per), (unsigned)((d + MOE_COLS - 1) / MOE_COLS));
+#define GO(TA, TW)                                                                                                 \
+    do {                                                                                                           \
+        if (smem > 48 * 1024)                                                                                      \
+            cudaFuncSetAttribute(moe_down_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        odin_launch(moe_down_kernel<TA, TW>, grid, dim3(MOE_THREADS), smem, s, (const TA*)a, (const TW*)w, ids,    \
+                    wts, T, per, ff, d, y);                                                                        \
+    } while (0)
+    if (a_dtype == ODIN_BF16 && w_dtype == ODIN_BF16) GO(bf16, bf16);
+    else if (a_dtype == ODIN_F32 && w_dtype == ODIN_F32) GO(float, float);
+    else if (a_dtype == ODIN_BF16 && w_dtype == ODIN_F32) GO(bf16, float);
+    else if (a_dtype == ODIN_F32 && w_dtype == ODIN_BF16) GO(float, bf16);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}

@@ -74,14 +74,14 @@ def _fn(group: str, name: str):
 
 
 # ----------------------------------------------------------------------------
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = table[ids[t], :] as 32-bit floats; ids int32 [T]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = table[ids[t], :] * scale as 32-bit floats; ids int32 [T]."""
     T, d = out.shape
     assert out.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == d
     assert table.is_contiguous() and out.is_contiguous()
     _check(_fn("elementwise", "odin_embed")(
         _ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(out), c_int(T), c_int(d),
-        c_int(table.shape[0]), _stream()), "embed")
+        c_int(table.shape[0]), c_float(scale), _stream()), "embed")
 
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -149,18 +149,42 @@ def _parts(t: torch.Tensor, rows: int, cols: int) -> tuple[int, int]:
     return (t.shape[0], rows * cols) if t.dim() == 3 else (1, 0)
 
 
-def row_update(x: torch.Tensor, delta: torch.Tensor | None, bias: torch.Tensor | None, weight: torch.Tensor | None,
+def row_update(x: torch.Tensor, delta, bias: torch.Tensor | None, weight: torch.Tensor | None,
                eps: float, groups: int, out: torch.Tensor | None, rows: torch.Tensor | None = None,
                normalise: bool = True) -> None:
     """x += sum of delta's parts + bias (in place, 32-bit; not with a row gather), then
     normalise: out = weight * x / rms, the root mean square taken over each of `groups` equal
     consecutive parts of the row by itself (out may be x: in place); else out = x converted
-    (out None: the update alone)."""
+    (out None: the update alone).  delta may be a list of up to three updates (each [n, d] or
+    [parts, n, d]; all but the first 32-bit), which are added in their order."""
     d = x.shape[-1]
     assert x.dtype == torch.float32 and x.is_contiguous()
+    more = []
+    if isinstance(delta, (list, tuple)):
+        delta, more = (delta[0], list(delta[1:])) if delta else (None, [])
     n_split, stride = (1, 0)
     if delta is not None:
         n_split, stride = _parts(delta, x.shape[0], d)
+    if more:
+        assert len(more) <= 2 and all(m.dtype == torch.float32 for m in more)
+        extra = []
+        for m in more + [None] * (2 - len(more)):
+            ns, st = _parts(m, x.shape[0], d) if m is not None else (0, 0)
+            extra += [_ptr(m), c_int(ns), c_longlong(st)]
+        if out is not None:
+            assert out.is_contiguous() and out.shape[-1] == d
+        n_rows = x.shape[0] if rows is None else rows.numel()
+        if rows is not None:
+            assert rows.dtype == torch.int32 and out is not None and out.shape[0] == n_rows
+        if normalise:
+            assert weight is not None and weight.numel() == d and out is not None and d % groups == 0
+        _check(_fn("rowwise", "odin_row_update_several")(
+            _ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype)), c_int(n_split), c_longlong(stride), *extra,
+            _ptr(bias), c_int(dtype_code(bias.dtype) if bias is not None else 0), _ptr(weight),
+            c_int(dtype_code(weight.dtype) if weight is not None else 0), c_float(eps), c_int(groups),
+            c_int(0 if normalise else 1), _ptr(out), c_int(dtype_code(out.dtype) if out is not None else 0), _ptr(rows),
+            c_int(n_rows), c_int(d), _stream()), "row_update")
+        return
     if out is not None:
         assert out.is_contiguous() and out.shape[-1] == d
     n_rows = x.shape[0] if rows is None else rows.numel()
@@ -203,6 +227,87 @@ def activation(src: torch.Tensor, kind: str, out: torch.Tensor, params: torch.Te
         _ptr(src), c_int(dtype_code(src.dtype)), c_int(n_split), c_longlong(stride), c_longlong(row),
         c_int(ACTIVATIONS[kind]), _ptr(params), c_int(dtype_code(params.dtype) if params is not None else 0), _ptr(out),
         c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), c_int(T), c_int(n), _stream()), "activation")
+
+
+def gated_activation(gate_up: torch.Tensor, kind: str, out: torch.Tensor) -> None:
+    """out[t, c] = act(gate[t, c]) * up[t, c] for gate_up = [T, 2 n] (the n gate columns first), or for the sum of
+    its leading parts when it is [parts, T, 2 n]; kind: silu (SwiGLU) or gelu_tanh (GeGLU)."""
+    T, n = out.shape
+    assert out.stride(1) == 1 and gate_up.stride(-1) == 1 and tuple(gate_up.shape[-2:]) == (T, 2 * n)
+    if gate_up.dim() == 3:
+        assert gate_up.is_contiguous()
+        n_split, stride, row = gate_up.shape[0], T * 2 * n, 2 * n
+    else:
+        n_split, stride, row = 1, 0, gate_up.stride(0)
+    _check(_fn("rowwise", "odin_gated_activation")(
+        _ptr(gate_up), c_int(dtype_code(gate_up.dtype)), c_int(n_split), c_longlong(stride), c_longlong(row),
+        c_int(ACTIVATIONS[kind]), _ptr(out), c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), c_int(T), c_int(n),
+        _stream()), "gated_activation")
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, n_heads: int, v_head_dim: int, per_head: bool) -> None:
+    """o[t, h, c] *= sigmoid(gate[t, h]) (per_head) or sigmoid(gate[t, h, c]), in place; gate: columns of a product's
+    output, [T, n] (a strided view is fine) or [parts, T, n] partial sums (a view of whole rows' columns)."""
+    T = o.shape[0]
+    n = n_heads if per_head else n_heads * v_head_dim
+    assert o.stride(1) == 1 and o.shape[1] == n_heads * v_head_dim and gate.stride(-1) == 1
+    assert tuple(gate.shape[-2:]) == (T, n)
+    if gate.dim() == 3:
+        n_split, stride, row = gate.shape[0], gate.stride(0), gate.stride(1)
+    else:
+        n_split, stride, row = 1, 0, gate.stride(0)
+    _check(_fn("rowwise", "odin_sigmoid_gate")(
+        _ptr(o), c_int(dtype_code(o.dtype)), c_longlong(o.stride(0)), _ptr(gate), c_int(dtype_code(gate.dtype)),
+        c_int(n_split), c_longlong(stride), c_longlong(row), c_int(1 if per_head else 0), c_int(T), c_int(n_heads),
+        c_int(v_head_dim), _stream()), "sigmoid_gate")
+
+
+def softcap(z: torch.Tensor, cap: float) -> None:
+    """z <- cap * tanh(z / cap) in place; z float32 [rows, n]."""
+    assert z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1
+    _check(_fn("rowwise", "odin_softcap")(_ptr(z), c_longlong(z.stride(0)), c_int(z.shape[0]), c_int(z.shape[1]),
+                                          c_float(cap), _stream()), "softcap")
+
+
+def moe_router(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: int, always: int,
+               tok_seq: torch.Tensor | None, ids: torch.Tensor, wts: torch.Tensor) -> None:
+    """Per token: logits W h + bias in 32-bit, the `top` largest chosen, weights = softmax over the chosen logits;
+    `always` further choices name the experts E, E + 1, ... with weight 1.  ids int32, wts float32: [T, top + always];
+    rows of sequence -1 get expert -1."""
+    T, d = h.shape
+    E = w.shape[0]
+    assert h.stride(1) == 1 and w.is_contiguous() and w.shape[1] == d
+    assert ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.is_contiguous() and wts.is_contiguous()
+    assert tuple(ids.shape) == tuple(wts.shape) == (T, top + always)
+    if bias is not None:
+        assert bias.numel() == E and bias.is_contiguous()
+    _check(_fn("moe", "odin_moe_router")(
+        _ptr(h), c_int(dtype_code(h.dtype)), c_longlong(h.stride(0)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(bias),
+        c_int(dtype_code(bias.dtype) if bias is not None else 0), c_int(T), c_int(E), c_int(d), c_int(top), c_int(always),
+        _ptr(tok_seq), _ptr(ids), _ptr(wts), _stream()), "moe_router")
+
+
+def moe_gate_up(h: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, kind: str, out: torch.Tensor) -> None:
+    """out[t * per + k, :] = act(Wg[e] h[t]) * (Wu[e] h[t]) with e = ids[t, k]; w: [experts, 2 ff, d], gate rows first."""
+    T, d = h.shape
+    per, ff = ids.shape[1], out.shape[1]
+    assert h.stride(1) == 1 and w.is_contiguous() and tuple(w.shape[1:]) == (2 * ff, d) and out.is_contiguous()
+    assert out.shape[0] == T * per and out.dtype == h.dtype and ids.dtype == torch.int32 and ids.is_contiguous()
+    _check(_fn("moe", "odin_moe_gate_up")(
+        _ptr(h), c_int(dtype_code(h.dtype)), c_longlong(h.stride(0)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(ids),
+        c_int(T), c_int(per), c_int(ff), c_int(d), c_int(ACTIVATIONS[kind]), _ptr(out), _stream()), "moe_gate_up")
+
+
+def moe_down(a: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, out: torch.Tensor) -> None:
+    """out[k, t, :] = wts[t, k] * Wd[e] a[t * per + k] with e = ids[t, k]; w: [experts, d, ff]; out float32 [per, T, d]:
+    partial sums of the tokens' update."""
+    T, per = ids.shape
+    ff, d = a.shape[1], w.shape[1]
+    assert a.is_contiguous() and a.shape[0] == T * per and w.is_contiguous() and w.shape[2] == ff
+    assert out.dtype == torch.float32 and out.is_contiguous() and tuple(out.shape) == (per, T, d)
+    _check(_fn("moe", "odin_moe_down")(
+        _ptr(a), c_int(dtype_code(a.dtype)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(ids), _ptr(wts), c_int(T),
+        c_int(per), c_int(ff), c_int(d), _ptr(out), _stream()), "moe_down")
 
 
 def gated_lookup(gate: torch.Tensor, kind: str, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor) -> None:
@@ -453,12 +558,12 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
     width = (n_q + n_kv) * head_dim + n_kv * vd
     if qkv.dim() == 3:
         n_split, T = qkv.shape[0], qkv.shape[1]
-        assert qkv.is_contiguous() and qkv.shape[2] == width
-        split_stride, row_stride = T * width, width
+        assert qkv.is_contiguous() and qkv.shape[2] >= width   # further columns (a gate's) are left alone
+        split_stride, row_stride = T * qkv.shape[2], qkv.shape[2]
         assert q_out is not None, "partial sums need a separate q_out"
     else:
         n_split, T, split_stride, row_stride = 1, qkv.shape[0], 0, qkv.stride(0)
-        assert qkv.stride(1) == 1 and qkv.shape[1] == width
+        assert qkv.stride(1) == 1 and qkv.shape[1] >= width
     if q_out is None:
         q_out = qkv[:, : n_q * head_dim]
     assert q_out.stride(1) == 1 and tuple(q_out.shape) == (T, n_q * head_dim)
@@ -492,8 +597,9 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
 def attention_plain(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                     k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
                     block_table: torch.Tensor, window: int = 0, chunk: int = 0, scale: float = 0.0,
-                    softcap: float = 0.0, v_head_dim: int | None = None) -> None:
+                    softcap: float = 0.0, v_head_dim: int | None = None, sink: torch.Tensor | None = None) -> None:
     """Causal attention of each token over its sequence's cache; q may be a strided view.
+    sink: float32 [n_q]; exp(sink[h]) joins the softmax's denominator of head h (no key, no value).
 
     window > 0: only the last `window` keys; chunk > 0: only the keys of the query's own chunk of
     `chunk` positions; scale > 0 replaces 1 / sqrt(head_dim); softcap > 0: scores pass through
@@ -508,7 +614,13 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, hea
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(dtype_code(q.dtype)),
         c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim), c_int(vd), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
         _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window), c_int(chunk),
-        c_float(scale), c_float(softcap), _stream()), "attention_plain")
+        c_float(scale), c_float(softcap), _ptr(_sink(sink, n_q)), _stream()), "attention_plain")
+
+
+def _sink(sink: torch.Tensor | None, n_q: int) -> torch.Tensor | None:
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_q
+    return sink
 
 
 def attention_decode_supported(head_dim: int) -> bool:

@@ -20,10 +20,17 @@
 // (out may be null: the update alone).
 // VEC: the row, a group and every distance between rows and parts are multiples of four elements and every
 // pointer is 16-byte aligned, so everything moves four elements at a time; the same sums in the same order.
+// more: up to two further updates (32-bit, each with parts of its own), added after `delta` in their order.
+struct MoreDeltas {
+    const float* p[2];
+    int n_split[2];
+    long long stride[2];
+};
+
 template <typename TD, typename TO, bool VEC>
 __global__ void __launch_bounds__(ROW_THREADS)
 row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t split_stride, VecRef bias, VecRef w,
-                  float eps, int groups, int mode, TO* out, const int* __restrict__ rows, int d) {
+                  float eps, int groups, int mode, TO* out, const int* __restrict__ rows, int d, MoreDeltas more) {
     __shared__ float red[32];
     extern __shared__ float rowbuf[];  // d floats
     pdl_trigger();
@@ -38,7 +45,7 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
         return;
     }
     float* xr = x + (size_t)src * d;
-    const bool updated = delta != nullptr || bias.p != nullptr;
+    const bool updated = delta != nullptr || bias.p != nullptr || more.p[0] != nullptr || more.p[1] != nullptr;
     const bool write_back = updated && rows == nullptr;
     if (VEC) {
         for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
@@ -48,6 +55,13 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
                     const float4 dv = ld4(delta + (size_t)s * split_stride + (size_t)src * d + j);
                     v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
                 }
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+                if (more.p[m] != nullptr)
+                    for (int s = 0; s < more.n_split[m]; ++s) {
+                        const float4 dv = ld4(more.p[m] + (size_t)s * more.stride[m] + (size_t)src * d + j);
+                        v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+                    }
             if (bias.p != nullptr) {
                 const float4 bv = bias.at4(j);
                 v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
@@ -59,6 +73,10 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
             float v = xr[j];
             if (delta != nullptr)
                 for (int s = 0; s < n_split; ++s) v += to_f32(delta[(size_t)s * split_stride + (size_t)src * d + j]);
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+                if (more.p[m] != nullptr)
+                    for (int s = 0; s < more.n_split[m]; ++s) v += more.p[m][(size_t)s * more.stride[m] + (size_t)src * d + j];
             if (bias.p != nullptr) v += bias.at(j);
             rowbuf[j] = v;
         }
@@ -118,9 +136,10 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
     }
 }
 
-extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
-                               const void* bias, int bias_dtype, const void* w, int w_dtype, float eps, int groups,
-                               int mode, void* out, int out_dtype, const int* rows, int n_rows, int d, void* stream) {
+static int row_update_launch(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
+                             const void* bias, int bias_dtype, const void* w, int w_dtype, float eps, int groups,
+                             int mode, void* out, int out_dtype, const int* rows, int n_rows, int d, MoreDeltas more,
+                             void* stream) {
     if (n_rows <= 0) return 0;
     if (d <= 0 || (mode != 0 && mode != 1)) return ODIN_ERR_BAD_ARG;
     if (mode == 0 && (groups <= 0 || d % groups != 0 || w == nullptr || out == nullptr)) return ODIN_ERR_BAD_ARG;
@@ -129,8 +148,10 @@ extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int
     cudaStream_t s = (cudaStream_t)stream;
     VecRef wv{w, w_dtype == ODIN_BF16}, bv{bias, bias_dtype == ODIN_BF16};
     const int gsz = mode == 0 ? d / groups : d;
-    const bool vec = (d % 4 == 0) && (gsz % 4 == 0) && (split_stride % 4 == 0) &&
-                     ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)bias) | ((uintptr_t)w) | ((uintptr_t)out)) % 16 == 0);
+    const bool vec = (d % 4 == 0) && (gsz % 4 == 0) && (split_stride % 4 == 0) && (more.stride[0] % 4 == 0) &&
+                     (more.stride[1] % 4 == 0) &&
+                     ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)bias) | ((uintptr_t)w) | ((uintptr_t)out) |
+                       ((uintptr_t)more.p[0]) | ((uintptr_t)more.p[1])) % 16 == 0);
 #define GO(TD, TO)                                                                                               \
     do {                                                                                                         \
         auto kern = vec ? row_update_kernel<TD, TO, true> : row_update_kernel<TD, TO, false>;                    \
@@ -139,7 +160,7 @@ extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int
             if (e != cudaSuccess) return (int)e;                                                                 \
         }                                                                                                        \
         odin_launch(kern, dim3(n_rows), dim3(ROW_THREADS), smem, s, x, (const TD*)delta, n_split,                 \
-                    (size_t)split_stride, bv, wv, eps, groups, mode, (TO*)out, rows, d);                         \
+                    (size_t)split_stride, bv, wv, eps, groups, mode, (TO*)out, rows, d, more);                   \
     } while (0)
     const bool dbf = delta != nullptr && delta_dtype == ODIN_BF16;
     if (out_dtype == ODIN_BF16) { if (dbf) GO(bf16, bf16); else GO(float, bf16); }
@@ -148,6 +169,25 @@ extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int
 #undef GO
     ODIN_LAUNCH_CHECK();
     return 0;
+}
+
+extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
+                               const void* bias, int bias_dtype, const void* w, int w_dtype, float eps, int groups,
+                               int mode, void* out, int out_dtype, const int* rows, int n_rows, int d, void* stream) {
+    MoreDeltas more{{nullptr, nullptr}, {0, 0}, {0, 0}};
+    return row_update_launch(x, delta, delta_dtype, n_split, split_stride, bias, bias_dtype, w, w_dtype, eps, groups, mode,
+                             out, out_dtype, rows, n_rows, d, more, stream);
+}
+
+// The same with up to two further 32-bit updates (null: none), each [parts][n, d], added after `delta`.
+extern "C" int odin_row_update_several(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
+                                       const float* delta2, int n_split2, long long split_stride2, const float* delta3,
+                                       int n_split3, long long split_stride3, const void* bias, int bias_dtype,
+                                       const void* w, int w_dtype, float eps, int groups, int mode, void* out,
+                                       int out_dtype, const int* rows, int n_rows, int d, void* stream) {
+    MoreDeltas more{{delta2, delta3}, {n_split2, n_split3}, {split_stride2, split_stride3}};
+    return row_update_launch(x, delta, delta_dtype, n_split, split_stride, bias, bias_dtype, w, w_dtype, eps, groups, mode,
+                             out, out_dtype, rows, n_rows, d, more, stream);
 }
 
 // ------------------------------------------------------------ x += w * (y / rms(y))
@@ -344,6 +384,109 @@ extern "C" int odin_gated_lookup(const void* gate, int gate_dtype, int n_split, 
     else if (gate_dtype == ODIN_F32 && table_dtype == ODIN_F32 && out_dtype == ODIN_BF16) GO(float, float, bf16);
     else return ODIN_ERR_UNSUPPORTED;
 #undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ gated activation of a gate|up product
+// out[t, c] = act(sum_s in[s][t, c]) * (sum_s in[s][t, n + c]) for a product whose row holds the n gate
+// columns before the n up columns (SiLU gives SwiGLU, tanh-GELU gives GeGLU); 32-bit arithmetic.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+gated_activation_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, size_t in_stride, int act,
+                        TO* __restrict__ out, size_t out_stride, int T, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)T * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / n), c = (int)(i % n);
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < n_split; ++s) {
+            const TI* row = in + (size_t)s * split_stride + (size_t)t * in_stride;
+            g += to_f32(row[c]);
+            u += to_f32(row[n + c]);
+        }
+        out[(size_t)t * out_stride + c] = from_f32<TO>(activate(act, g, 0.f, 0.f) * u);
+    }
+}
+
+extern "C" int odin_gated_activation(const void* in, int in_dtype, int n_split, long long split_stride, long long in_stride,
+                                     int act, void* out, int out_dtype, long long out_stride, int T, int n, void* stream) {
+    if (T <= 0 || n <= 0) return 0;
+    if (act < 0 || act > ACT_GELU_TANH) return ODIN_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)T * n;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+#define GO(TI, TO)                                                                                                   \
+    odin_launch(gated_activation_kernel<TI, TO>, dim3(blocks), dim3(256), 0, s, (const TI*)in, n_split,              \
+                (size_t)split_stride, (size_t)in_stride, act, (TO*)out, (size_t)out_stride, T, n)
+    if (in_dtype == ODIN_F32 && out_dtype == ODIN_F32) GO(float, float);
+    else if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16) GO(float, bf16);
+    else if (in_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(bf16, bf16);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ sigmoid gate on the heads of a mixer's output
+// o[t, h * vd + c] *= sigmoid(sum_s gate[s][t, per_head ? h : h * vd + c]): one gate per element, or one per head.
+// gate: columns of a (possibly split) product's output, row distance gate_stride; the sigmoid in 32-bit.
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(TO* __restrict__ o, size_t o_stride, const TG* __restrict__ gate, int n_split, size_t split_stride,
+                    size_t gate_stride, int per_head, int T, int H, int vd) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = H * vd;
+    const long long total = (long long)T * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / n), c = (int)(i % n);
+        const int gc = per_head ? c / vd : c;
+        float z = 0.f;
+        for (int s = 0; s < n_split; ++s) z += to_f32(gate[(size_t)s * split_stride + (size_t)t * gate_stride + gc]);
+        TO* p = o + (size_t)t * o_stride + c;
+        *p = from_f32<TO>(to_f32(*p) / (1.0f + expf(-z)));
+    }
+}
+
+extern "C" int odin_sigmoid_gate(void* o, int o_dtype, long long o_stride, const void* gate, int gate_dtype, int n_split,
+                                 long long split_stride, long long gate_stride, int per_head, int T, int H, int vd,
+                                 void* stream) {
+    if (T <= 0 || H <= 0 || vd <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long total = (long long)T * H * vd;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+#define GO(TG, TO)                                                                                                   \
+    odin_launch(sigmoid_gate_kernel<TG, TO>, dim3(blocks), dim3(256), 0, s, (TO*)o, (size_t)o_stride, (const TG*)gate, \
+                n_split, (size_t)split_stride, (size_t)gate_stride, per_head, T, H, vd)
+    if (gate_dtype == ODIN_F32 && o_dtype == ODIN_F32) GO(float, float);
+    else if (gate_dtype == ODIN_F32 && o_dtype == ODIN_BF16) GO(float, bf16);
+    else if (gate_dtype == ODIN_BF16 && o_dtype == ODIN_BF16) GO(bf16, bf16);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ cap on 32-bit values, in place
+// z <- cap * tanh(z / cap)
+__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ z, size_t stride, int rows, int n, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)rows * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float* p = z + (size_t)(i / n) * stride + (i % n);
+        *p = cap * tanhf(*p / cap);
+    }
+}
+
+extern "C" int odin_softcap(float* z, long long stride, int rows, int n, float cap, void* stream) {
+    if (rows <= 0 || n <= 0) return 0;
+    if (!(cap > 0.f)) return ODIN_ERR_BAD_ARG;
+    const long long total = (long long)rows * n;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    odin_launch(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, z, (size_t)stride, rows, n, cap);
     ODIN_LAUNCH_CHECK();
     return 0;
 }

@@ -195,12 +195,16 @@ class Runtime:
         ops.gemm_plain(a, w, out)
         return out
 
-    def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, inner: int) -> torch.Tensor:
+    def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, inner: int, activation: str = "silu") -> torch.Tensor:
         """silu(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu]: one kernel with the SwiGLU in its
         epilogue for many bfloat16 tokens, else the product followed by the SwiGLU kernel
-        (which also adds the partial sums of a split product)."""
+        (which also adds the partial sums of a split product).  Another activation of the gate
+        (gelu_tanh) runs as the product followed by the gated-activation kernel."""
         M = a.shape[0]
         act = self.empty(M, inner)
+        if activation != "silu":
+            ops.gated_activation(self.linear(a, w_gate_up, out_dtype=torch.float32, may_split=True), activation, act)
+            return act
         # From 129 tokens on the pair kernel with the SwiGLU in its epilogue: the gate|up weight has tiles
         # enough for the pairs of SMs even beside one tile of 256 tokens, and no partial sums are written
         # (measured against the weights-wide kernel + SwiGLU kernel: 8 to 10 % of the step at 129 to 256 tokens).
@@ -213,6 +217,21 @@ class Runtime:
             return act
         ops.swiglu(self.linear(a, w_gate_up, may_split=True), act)
         return act
+
+    # ---- experts chosen per token ----------------------------------------
+    def experts(self, h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
+                wts: torch.Tensor, activation: str) -> torch.Tensor:
+        """The chosen experts' gated feed-forwards for every (token, choice): ids / wts [T, per] name each
+        choice's expert (-1: none) and weight; w_gate_up [experts, 2 inner, width], w_down [experts, width,
+        inner].  Returns float32 [per, T, width]: slice k holds every token's k-th choice, weighted; partial
+        sums of the update."""
+        T, per = ids.shape
+        inner, width = w_down.shape[2], w_down.shape[1]
+        a = self.empty(T * per, inner)
+        ops.moe_gate_up(h, w_gate_up, ids, activation, a)
+        y = self.empty(per, T, width, dtype=torch.float32)
+        ops.moe_down(a, w_down, ids, wts, y)
+        return y
 
     # ---- attention over the cache ---------------------------------------
     def attention_with_head_prep(self, step, qkv, out, n_q, n_kv, head_dim, q_norm, k_norm, eps, cos, sin,
@@ -244,13 +263,16 @@ class Runtime:
         return out
 
     def attention(self, step, q, out, n_q, n_kv, head_dim, k_line, v_line, block_table, window, chunk: int = 0,
-                  scale: float = 0.0, softcap: float = 0.0, v_head_dim: int | None = None) -> None:
+                  scale: float = 0.0, softcap: float = 0.0, v_head_dim: int | None = None, sink=None) -> None:
         """bfloat16: one token per sequence goes to the split-key kernel, prompts (and pieces
         of prompts) to the flash kernel.  The 32-bit path and head sizes that the fast
         kernels refuse go to the plain kernel, and so do value heads of another size than the keys'.
         chunk, scale, softcap: a chunk mask, a factor on q . k other than 1 / sqrt(head_dim), a cap on
-        the scores; every kernel takes them."""
+        the scores; every kernel takes them.  sink: float32 [n_q], a logit per head that joins the softmax's
+        denominator."""
         same_heads = (v_head_dim or head_dim) == head_dim   # the fast kernels' value heads have the keys' size
+        if sink is not None:
+            same_heads = False
         if self.dtype == torch.bfloat16 and same_heads and step.all_single and ops.attention_decode_supported(head_dim):
             B = q.shape[0]
             n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms)
@@ -263,4 +285,4 @@ class Runtime:
                                   step.seq_start, step.seq_len_after, block_table, window, chunk, scale, softcap)
             return
         ops.attention_plain(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
-                            window, chunk, scale, softcap, v_head_dim)
+                            window, chunk, scale, softcap, v_head_dim, sink)

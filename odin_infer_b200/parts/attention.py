@@ -24,6 +24,10 @@ class GQAttention(Mixer):
     biases: names of bias vectors of the projections ({"q", "k", "v", "o"}), added in the projection.
     scale: factor on q . k (0: 1 / sqrt(head_dim)).  softcap > 0: scores become
     softcap * tanh(score / softcap) before the softmax.  v_head_dim: size of a value head (0: head_dim).
+    sink: name of a tensor [n_q_heads]: a learned logit per query head whose exponential joins the softmax's
+    denominator (no key, no value, not scaled).  gate: name of a matrix G; the heads' outputs are multiplied by
+    sigmoid(G h) before the output projection, one factor per element (G: [n_q_heads * v_head_dim, width]) or,
+    with gate_per_head, one per head (G: [n_q_heads, width]); G is fused with q, k and v into one product.
     """
 
     graph_safe = True
@@ -31,7 +35,8 @@ class GQAttention(Mixer):
     def __init__(self, width: int, n_q_heads: int, n_kv_heads: int, head_dim: int, names: dict,
                  position_encoding: str | None = None, qk_norm=True, eps: float = 1e-6,
                  window: int = 0, kv_shared: bool = False, chunk: int = 0, biases: dict | None = None,
-                 scale: float = 0.0, softcap: float = 0.0, v_head_dim: int = 0):
+                 scale: float = 0.0, softcap: float = 0.0, v_head_dim: int = 0, sink: str | None = None,
+                 gate: str | None = None, gate_per_head: bool = False):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads are not a multiple of {n_kv_heads} kv heads")
         if qk_norm not in (True, False, "unit_after"):
@@ -44,8 +49,12 @@ class GQAttention(Mixer):
         self.chunk, self.scale, self.softcap = int(chunk), float(scale), float(softcap)
         self.bias_names = dict(biases) if biases else None
         # the heads as the first architecture has them: the fast kernels' ground
+        self.sink_name, self.gate_name, self.gate_per_head = sink, gate, bool(gate_per_head)
+        self.n_gate = 0 if gate is None else (self.n_q if self.gate_per_head else self.n_q * self.vd)
         self.plain_heads = (self.bias_names is None and not self.unit_after and self.vd == self.hd
-                            and self.chunk == 0 and self.scale == 0.0 and self.softcap == 0.0)
+                            and self.chunk == 0 and self.scale == 0.0 and self.softcap == 0.0
+                            and sink is None and gate is None)
+        self.sink = None
         self.pe = None          # set by the model from pe_name
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.b_qkv = self.b_o = None
         self._dummy = None
@@ -67,17 +76,27 @@ class GQAttention(Mixer):
             if not self.kv_shared:
                 out += [ParamSpec(b["k"], (self.n_kv * self.hd,)), ParamSpec(b["v"], (self.n_kv * self.vd,))]
             out.append(ParamSpec(b["o"], (self.width,)))
+        if self.sink_name is not None:
+            out.append(ParamSpec(self.sink_name, (self.n_q,), init="logit"))
+        if self.gate_name is not None:
+            out.append(ParamSpec(self.gate_name, (self.n_gate, self.width)))
         return out
 
     def bind(self, tensors, rt):
         n = self.names
-        if self.kv_shared:
+        if self.kv_shared and self.gate_name is None:
             self.w_qkv = tensors[n["q"]]
         else:
-            q, k, v = tensors.pop(n["q"]), tensors.pop(n["k"]), tensors.pop(n["v"])
-            if not (q.dtype == k.dtype == v.dtype):
-                q, k, v = (t.to(torch.float32) for t in (q, k, v))
-            self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+            mats = [tensors.pop(n["q"])] if not self.kv_shared else [tensors[n["q"]]]
+            if not self.kv_shared:
+                mats += [tensors.pop(n["k"]), tensors.pop(n["v"])]
+            if self.gate_name is not None:
+                mats.append(tensors.pop(self.gate_name))
+            if len({t.dtype for t in mats}) > 1:
+                mats = [t.to(torch.float32) for t in mats]
+            self.w_qkv = torch.cat(mats, dim=0).contiguous()
+        if self.sink_name is not None:
+            self.sink = tensors[self.sink_name].to(torch.float32).contiguous()
         self.w_o = tensors[n["o"]]
         if self.qk_norm:
             self.q_norm = tensors[n["q_norm"]]
@@ -97,7 +116,7 @@ class GQAttention(Mixer):
         return KVRequest(self.n_kv, self.hd, self.window, self.chunk, self.vd if self.vd != self.hd else 0)
 
     def kernel_groups(self):
-        return {"head_prep", "attention_plain", "gemm_plain"}
+        return {"head_prep", "attention_plain", "gemm_plain"} | ({"rowwise"} if self.gate_name is not None else set())
 
     def notes(self, rt):
         import torch
@@ -141,7 +160,10 @@ class GQAttention(Mixer):
                               write_kv=writes, q_out=q_out, bias=self.b_qkv, unit_norm_after=self.unit_after,
                               v_head_dim=self.vd)
             rt.attention(step, q, o, self.n_q, self.n_kv, self.hd, k_line, v_line, block_table, self.window,
-                         chunk=self.chunk, scale=self.scale, softcap=self.softcap, v_head_dim=self.vd)
+                         chunk=self.chunk, scale=self.scale, softcap=self.softcap, v_head_dim=self.vd, sink=self.sink)
+            if self.gate_name is not None:
+                g0 = qkv.shape[-1] - self.n_gate
+                ops.sigmoid_gate(o, qkv[..., g0:], self.n_q, self.vd, self.gate_per_head)
             out = rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True, add_to=residual)
             return out if self.b_o is None else Biased(out, self.b_o)
         # decoding: the attention kernel may prepare its heads itself

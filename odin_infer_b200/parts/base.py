@@ -35,7 +35,8 @@ from ..cache import KVRequest
 class ParamSpec:
     """One tensor of the model folder.
 
-    init: how random-weights mode fills it: "matrix" N(0, 0.02), "norm" 1 + N(0, 0.1),
+    init: how random-weights mode fills it: "matrix" N(0, 0.02), "norm" 1 + N(0, 0.1), "near_zero" N(0, 0.1),
+    "logit" N(0, 1),
     "unit" 0.5 + N(0, 0.15) (mixing weights and lower bounds between 0 and 1), "decay"
     -2 + N(0, 1) (what a double exponential turns into a decay), "zeros", or "int_table"
     (int32 zeros).  alias_of: the name of another tensor that stands in when this one is
@@ -110,13 +111,23 @@ class Biased:
         self.update, self.bias = update, bias
 
 
+class Several(list):
+    """Several updates of the residual stream that are pending at once (a block whose mixer and feed-forward
+    read the same input answers both): tensors [n, width] or [parts, n, width], added in their order.  Only a
+    norm that says `takes_several` may follow; it gets them as a list in place of `delta`."""
+
+
 def split_update(pending):
-    """(delta, bias) of what a mixer or feed-forward answered: each a tensor or None."""
+    """(delta, bias) of what a mixer or feed-forward answered: each a tensor or None (delta a list of
+    tensors for `Several`)."""
     bias = None
     if isinstance(pending, Biased):
         pending, bias = pending.update, pending.bias
     if isinstance(pending, ResidualAdded):
         pending = None
+    if isinstance(pending, Several):
+        kept = [u for u in pending if u is not None and not isinstance(u, ResidualAdded)]
+        pending = None if not kept else kept[0] if len(kept) == 1 else kept
     return pending, bias
 
 
@@ -130,6 +141,7 @@ class Norm(Part):
         raise NotImplementedError
 
     takes_bias = False
+    takes_several = False   # `delta` may be a list of up to three updates
 
 
 class PositionEncoding(Part):

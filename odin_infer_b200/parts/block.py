@@ -1,7 +1,7 @@
 """How a layer's parts are arranged."""
 from __future__ import annotations
 
-from .base import Block, PartSpec, build_part, register_part, split_update
+from .base import Block, PartSpec, ResidualAdded, Several, build_part, register_part, split_update
 
 
 @register_part("block", "prenorm")
@@ -67,3 +67,36 @@ class PreNormBlock(Block):
             x, pending = extra.forward(rt, step, x, pending)
         delta, bias = split_update(pending)
         return x, (pending if bias is not None else delta)
+
+
+@register_part("block", "parallel")
+class ParallelBlock(PreNormBlock):
+    """h = Norm(x);  x -> x + Mixer(h) + FeedForward(h): one norm, and both sublayers read its output.
+    A block may have no feed-forward.
+
+    Both updates stay pending (`Several`) and are added, in the order mixer, feed-forward, by the norm
+    that runs next; a sublayer whose last product has added itself to x in its epilogue leaves nothing."""
+
+    def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, norm: PartSpec):
+        self._mixer = build_part("mixer", mixer)
+        self.ffn = build_part("feed_forward", feed_forward) if feed_forward is not None else None
+        self.norm_mixer = build_part("norm", norm)
+        self.norm_ffn = None
+        self.extras = []
+        if not self.norm_mixer.takes_several:
+            raise TypeError(f"{type(self.norm_mixer).__name__} cannot add several pending updates")
+
+    def forward(self, rt, step, x, pending, entry):
+        mixer, ffn = self._mixer, self.ffn
+        h = self._norm(self.norm_mixer, rt, x, pending)
+        # h is computed: a product that adds to x in its epilogue no longer changes what the sublayers read
+        out = [mixer.forward(rt, step, h, entry, residual=x) if mixer.takes_residual else mixer.forward(rt, step, h, entry)]
+        if ffn is not None:
+            out.append(ffn.forward(rt, step, h, residual=x) if ffn.takes_residual else ffn.forward(rt, step, h))
+        pending = Several()
+        for upd in out:
+            if isinstance(upd, Several):
+                pending.extend(upd)
+            elif not isinstance(upd, ResidualAdded):
+                pending.append(upd)
+        return x, (pending if pending else None)

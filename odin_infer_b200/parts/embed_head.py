@@ -9,13 +9,14 @@ from .base import Embedding, Head, ParamSpec, PartSpec, build_part, register_par
 
 @register_part("embedding", "token_table")
 class TokenEmbedding(Embedding):
-    """x = E[token], no scaling (infer/forward.odin:43).  norm: a norm (a PartSpec of a norm that can
-    work in place) through which the embedded rows pass before they become the residual stream."""
+    """x = E[token] (infer/forward.odin:43), times `scale` (a 32-bit product) where one is given.  norm: a norm
+    (a PartSpec of a norm that can work in place) through which the embedded rows pass before they become the
+    residual stream."""
 
     graph_safe = True
 
-    def __init__(self, vocab_size: int, width: int, weight: str, norm: PartSpec | None = None):
-        self.vocab_size, self.width, self.weight_name = vocab_size, width, weight
+    def __init__(self, vocab_size: int, width: int, weight: str, norm: PartSpec | None = None, scale: float = 1.0):
+        self.vocab_size, self.width, self.weight_name, self.scale = vocab_size, width, weight, float(scale)
         self.norm = build_part("norm", norm) if norm is not None else None
         self.table = None
 
@@ -32,7 +33,7 @@ class TokenEmbedding(Embedding):
 
     def forward(self, rt, step):
         x = rt.empty(step.n_rows, self.width, dtype=torch.float32)
-        ops.embed(self.table, step.tok_ids, x)
+        ops.embed(self.table, step.tok_ids, x, self.scale)
         if self.norm is not None:
             self.norm.in_place(rt, x)
         return x
@@ -41,12 +42,14 @@ class TokenEmbedding(Embedding):
 @register_part("head", "linear")
 class LinearHead(Head):
     """logits = W h, 32-bit out; W is its own tensor or, when `tied_to` is given and
-    the folder has no such tensor, the embedding table (infer/model.odin:150-158)."""
+    the folder has no such tensor, the embedding table (infer/model.odin:150-158).
+    softcap > 0: logits <- softcap * tanh(logits / softcap)."""
 
     graph_safe = True
 
-    def __init__(self, vocab_size: int, width: int, weight: str, tied_to: str | None = None):
+    def __init__(self, vocab_size: int, width: int, weight: str, tied_to: str | None = None, softcap: float = 0.0):
         self.vocab_size, self.width, self.weight_name, self.tied_to = vocab_size, width, weight, tied_to
+        self.softcap = float(softcap)
         self.w = None
 
     def params(self):
@@ -56,7 +59,10 @@ class LinearHead(Head):
         self.w = tensors[self.weight_name]
 
     def kernel_groups(self):
-        return {"gemm_plain"}
+        return {"gemm_plain"} | ({"rowwise"} if self.softcap > 0 else set())
 
     def forward(self, rt, step, h):
-        return rt.linear(h, self.w, out_dtype=torch.float32)
+        logits = rt.linear(h, self.w, out_dtype=torch.float32)
+        if self.softcap > 0:
+            ops.softcap(logits, self.softcap)
+        return logits

@@ -10,12 +10,15 @@ from .base import FeedForward, ParamSpec, register_part
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
     """down( silu(gate(x)) * up(x) ), no bias (infer/forward.odin:125-135).  The gate
-    and up matrices are fused into one at load time."""
+    and up matrices are fused into one at load time.  activation: "silu", or "gelu_tanh" for
+    down( gelu_tanh(gate(x)) * up(x) )."""
 
     graph_safe = True
 
-    def __init__(self, width: int, inner: int, names: dict):
-        self.width, self.inner, self.names = width, inner, dict(names)
+    def __init__(self, width: int, inner: int, names: dict, activation: str = "silu"):
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"a gated feed-forward takes silu or gelu_tanh, got '{activation}'")
+        self.width, self.inner, self.names, self.activation = width, inner, dict(names), activation
         self.w_gate_up = self.w_down = None
 
     def params(self):
@@ -32,7 +35,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors[n["down"]]
 
     def kernel_groups(self):
-        return {"elementwise", "gemm_plain"}
+        return {"elementwise", "gemm_plain"} | ({"rowwise"} if self.activation != "silu" else set())
 
     def notes(self, rt):
         if rt.dtype != torch.bfloat16:
@@ -44,7 +47,7 @@ class SwiGLU(FeedForward):
     takes_residual = True
 
     def forward(self, rt, step, h, residual=None):
-        act = rt.gated_linear(h, self.w_gate_up, self.inner)
+        act = rt.gated_linear(h, self.w_gate_up, self.inner, self.activation)
         return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True, add_to=residual)
 
 

@@ -12,22 +12,28 @@ class RMSNorm(Norm):
     """o = w * (x / sqrt(mean(x^2) + eps)), in 32-bit (infer/ops.odin:7-19).
 
     groups > 1: the row is cut into that many equal consecutive parts and each part is divided
-    by its own root mean square; the weight still spans the whole row."""
+    by its own root mean square; the weight still spans the whole row.
+    one_plus: the stored weight lies around zero and the factor is 1 + w (the sum is formed once at load,
+    in 32-bit, and kept so)."""
 
     graph_safe = True
     takes_bias = True
+    takes_several = True
 
-    def __init__(self, width: int, eps: float, weight: str, groups: int = 1):
+    def __init__(self, width: int, eps: float, weight: str, groups: int = 1, one_plus: bool = False):
         if groups < 1 or width % groups:
             raise ValueError(f"a norm over {width} elements cannot be cut into {groups} equal groups")
         self.width, self.eps, self.weight_name, self.groups = width, float(eps), weight, int(groups)
+        self.one_plus = bool(one_plus)
         self.weight: torch.Tensor | None = None
 
     def params(self):
-        return [ParamSpec(self.weight_name, (self.width,), init="norm")]
+        return [ParamSpec(self.weight_name, (self.width,), init="near_zero" if self.one_plus else "norm")]
 
     def bind(self, tensors, rt):
         self.weight = tensors[self.weight_name]
+        if self.one_plus:
+            self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()
 
     def kernel_groups(self):
         return {"elementwise", "rowwise"}
@@ -35,7 +41,9 @@ class RMSNorm(Norm):
     def forward(self, rt, x, delta, rows=None, bias=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = rt.empty(n, self.width)
-        if self.groups == 1 and bias is None:
+        if isinstance(delta, (list, tuple)) and len(delta) == 1:
+            delta = delta[0]
+        if self.groups == 1 and bias is None and not isinstance(delta, (list, tuple)):
             ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
         else:
             ops.row_update(x, delta, bias, self.weight, self.eps, self.groups, out, rows)

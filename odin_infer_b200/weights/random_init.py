@@ -1,7 +1,8 @@
 """Random-weights mode: a model folder (config.json, model.safetensors) from a
 configuration and a seed, or the same tensors straight in memory.
 
-Matrices are N(0, 0.02), norm weights 1 + N(0, 0.1), integer tables zero.
+Matrices are N(0, 0.02), norm weights 1 + N(0, 0.1) (N(0, 0.1) where the norm adds the one itself), logits
+that stand alone (an attention sink, a router's bias) N(0, 1), integer tables zero.
 
 The generator is counter-based: element i of the tensor called `name` under `seed` is a
 function of (seed, name, i) alone, so a tensor's values do not depend on which other
@@ -36,7 +37,8 @@ from .safetensors_io import write_safetensors
 _M64 = (1 << 64) - 1
 _SIGMA_S = math.sqrt(8.0 * (65536.0 ** 2 - 1.0) / 12.0)
 _CENTER = 4 * 65535
-_INIT = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1), "unit": (0.5, 0.15), "decay": (-2.0, 1.0)}   # mean, standard deviation
+_INIT = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1), "unit": (0.5, 0.15), "decay": (-2.0, 1.0),
+         "near_zero": (0.0, 0.1), "logit": (0.0, 1.0)}   # mean, standard deviation
 
 
 def _mix64(z: int) -> int:
