@@ -37,7 +37,7 @@ def build_nufupel_spec(cfg: NufupelConfig) -> ModelSpec:
             if l.rot_dims > 0:
                 pe = f"rope_{l.rot_dims}_{l.rot_base!r}_{l.rot_scaling!r}"
                 stretch = dict(zip(("factor", "low", "high", "original"), l.rot_scaling)) if l.rot_scaling else None
-                encodings[pe] = PartSpec("rope", dict(rotary_dim=l.rot_dims, theta=l.rot_base, stretch=stretch))
+                encodings[pe] = PartSpec("rope", dict(rotary_dim=l.rot_dims, theta=l.rot_base, stretch=stretch, precise=True))
         mixer = PartSpec("gqa_attention", dict(
             width=cfg.width, n_q_heads=l.heads, n_kv_heads=l.kv_heads, head_dim=l.dim, v_head_dim=l.vdim,
             position_encoding=pe, qk_norm=qk_norm, eps=cfg.norm_eps, window=l.window, scale=l.scale, names=names,

@@ -245,7 +245,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 // out[t][h][:] = sum_s w_s acc_s / sum_s w_s l_s, w_s = 2^(m_s - max m)
 __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int n_split,
                                     int hd, bf16* __restrict__ out, size_t out_stride, int Hq,
-                                    const int* __restrict__ tok_seq) {
+                                    const int* __restrict__ tok_seq, const float* __restrict__ sink) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x / Hq, h = blockIdx.x % Hq;
@@ -255,7 +255,9 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const fl
     float mm = NEG_BIG;
     for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, ml[2 * s]);
     float ll = 0.f;
+    if (sink != nullptr) mm = fmaxf(mm, sink[h] * 1.4426950408889634f);   // the sink's logit joins the denominator alone
     for (int s = 0; s < n_split; ++s) ll += ml[2 * s + 1] * exp2f(ml[2 * s] - mm);
+    if (sink != nullptr) ll += exp2f(sink[h] * 1.4426950408889634f - mm);
     const float inv = ll > 0.f ? 1.0f / ll : 0.f;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float a = 0.f;
@@ -270,6 +272,7 @@ struct ScoreOpts {
     int chunk = 0;
     float scale = 0.f;
     float softcap = 0.f;
+    const float* sink = nullptr;   // one logit per query head that joins the softmax's denominator
     float scale_log2(int hd) const { return 1.4426950408889634f * (scale > 0.f ? scale : 1.0f / sqrtf((float)hd)); }
     float cap_log2() const { return softcap > 0.f ? 1.4426950408889634f * softcap : 0.f; }
 };
@@ -297,7 +300,7 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, 
 #undef GO
     ODIN_LAUNCH_CHECK();
     odin_launch(attn_combine_kernel, dim3(B * Hq), dim3(HD < 128 ? 32 : 128), 0, s, (const float*)part_acc,
-                (const float*)part_ml, n_split, (int)HD, out, out_stride, Hq, tok_seq);
+                (const float*)part_ml, n_split, (int)HD, out, out_stride, Hq, tok_seq, so.sink);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
@@ -378,6 +381,7 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
     p.scale_log2 = so.scale_log2(HD);
     p.chunk = so.chunk;
     p.cap_log2 = so.cap_log2();
+    p.sink = so.sink;
     p.part_acc = part_acc; p.part_ml = part_ml; p.n_split = n_split;
     p.error = decode_error_flag();
     p.counters = split_counters();
@@ -442,16 +446,18 @@ extern "C" int odin_attention_decode_supported(int hd) {
 // at position tok_pos[t].  n_pages: pages of the cache line (0: unknown, the tensor-core
 // kernel is then not used).  scratch: odin_attention_decode_scratch(...) floats.
 // odin_attention_decode_masked: the same with a chunk mask (chunk > 0: only the keys of the query's own chunk of
-// that many positions), a factor on q . k of the caller's (scale > 0) and capped scores (softcap > 0).
+// that many positions), a factor on q . k of the caller's (scale > 0), capped scores (softcap > 0) and a sink
+// (not null: one 32-bit logit per query head whose exponential joins the softmax's denominator).
 extern "C" int odin_attention_decode_masked(const void* q, long long q_row_stride, void* out, long long out_row_stride,
                                             int B, int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache,
                                             int page_size, int n_pages, const int* tok_pos, const int* tok_seq,
                                             const int* block_table, int bt_stride, int window, int chunk, float scale,
-                                            float softcap, float* scratch, int n_split, void* stream) {
+                                            float softcap, const float* sink, float* scratch, int n_split,
+                                            void* stream) {
     if (B <= 0) return 0;
     if (chunk < 0 || scale < 0.f || softcap < 0.f) return ODIN_ERR_BAD_ARG;
     ScoreOpts so;
-    so.chunk = chunk; so.scale = scale; so.softcap = softcap;
+    so.chunk = chunk; so.scale = scale; so.softcap = softcap; so.sink = sink;
     if (Hkv <= 0 || Hq % Hkv != 0 || n_split < 1 || scratch == nullptr) return ODIN_ERR_BAD_ARG;
     if (B > 65535 || Hq > 65535 || n_split > 65535) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -489,7 +495,7 @@ extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void
                                      int n_pages, const int* tok_pos, const int* tok_seq, const int* block_table,
                                      int bt_stride, int window, float* scratch, int n_split, void* stream) {
     return odin_attention_decode_masked(q, q_row_stride, out, out_row_stride, B, Hq, Hkv, hd, k_cache, v_cache, page_size,
-                                        n_pages, tok_pos, tok_seq, block_table, bt_stride, window, 0, 0.f, 0.f, scratch,
+                                        n_pages, tok_pos, tok_seq, block_table, bt_stride, window, 0, 0.f, 0.f, nullptr, scratch,
                                         n_split, stream);
 }
 

@@ -28,6 +28,7 @@ struct DecodeTcParams {
     int chunk;        // > 0: only the keys of the query's own chunk of this many positions
     float scale_log2;
     float cap_log2;   // > 0: scores (in log2 units) become cap_log2 * tanh(score / cap_log2)
+    const float* sink;  // not null: exp(sink[h]) joins the denominator of query head h (no key, no value, not scaled)
     float* part_acc;
     float* part_ml;
     int n_split;
@@ -56,6 +57,16 @@ struct DecodeTcParams {
 template <int BAR>
 __device__ __forceinline__ void group_sync() {
     asm volatile("bar.sync %0, 128;" ::"n"(BAR) : "memory");
+}
+
+// The sink's share of a finished row: its logit (natural units) against the row's maximum mm (log2 units);
+// the sum ll and the accumulators are rescaled when the sink is the larger.
+__device__ __forceinline__ void add_sink(float sink, float mm, float& ll, float4& a) {
+    const float sk = sink * 1.4426950408889634f;
+    const float m2 = fmaxf(mm, sk);
+    const float c = exp2f(mm - m2);
+    ll = ll * c + exp2f(sk - m2);
+    a.x *= c; a.y *= c; a.z *= c; a.w *= c;
 }
 
 template <int HD, int BAR>
@@ -93,6 +104,7 @@ __device__ __forceinline__ void split_arrive_and_combine(const DecodeTcParams& p
                 }
             }
         }
+        if (p.sink != nullptr) add_sink(p.sink[h0 + r], mm, ll, a);
         const float inv = ll > 0.f ? 1.0f / ll : 0.f;
         uint2 u2;
         u2.x = attn::pack_bf16(a.x * inv, a.y * inv);
@@ -446,6 +458,7 @@ __device__ __forceinline__ void attn_decode_tc_body(const CUtensorMap& map_k, co
             mm = fmaxf(mm, s_ml[(w * 16 + r) * 2]);
         }
         if (p.n_split == 1) {
+            if (p.sink != nullptr) add_sink(p.sink[h0 + r], mm, ll, a);
             const float inv = ll > 0.f ? 1.0f / ll : 0.f;
             uint2 u;
             u.x = pack_bf16(a.x * inv, a.y * inv);

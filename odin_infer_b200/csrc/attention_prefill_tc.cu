@@ -67,6 +67,7 @@ struct PrefillTcParams {
     int chunk;        // > 0: a query sees only the keys of its own chunk of this many positions
     float scale_log2;
     float cap_log2;   // > 0: scores (in log2 units) become cap_log2 * tanh(score / cap_log2)
+    const float* sink;  // not null: exp(sink[h]) joins the denominator of query head h (no key, no value, not scaled)
     int* error;
     int n_heads, n_seqs, n_tile_levels;  // the work: (head, sequence, tile) triples, heaviest tile level first
 };
@@ -432,7 +433,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // the row's sum is the pair's two shares
             s_max[half * 128 + row] = l_run;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-            const float l_all = l_run + s_max[(half ^ 1) * 128 + row];
+            float l_all = l_run + s_max[(half ^ 1) * 128 + row];
+            // the sink's share, against the maximum that the sums are scaled by (both threads of a row hold the same)
+            if (p.sink != nullptr && m_run != -CUDART_INF_F) l_all += ex2(fmaf(p.sink[h], 1.4426950408889634f, -m_run));
             const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             bf16* dst = p.out + (size_t)(tok0 + q0 + row) * p.out_stride + (size_t)h * HD;
 #pragma unroll 1
@@ -513,12 +516,14 @@ int launch_prefill_tc(const CUtensorMap& mk, const CUtensorMap& mv, const Prefil
 }  // namespace
 
 // The output rows must be 16-byte aligned.  chunk > 0: a query sees only the keys of its own chunk of that
-// many positions; scale > 0 replaces 1 / sqrt(hd); softcap > 0: scores become softcap * tanh(score / softcap).
+// many positions; scale > 0 replaces 1 / sqrt(hd); softcap > 0: scores become softcap * tanh(score / softcap);
+// sink (not null): one 32-bit logit per query head whose exponential joins the softmax's denominator.
 extern "C" int odin_attention_prefill_tc_masked(const void* q, long long q_row_stride, void* out, long long out_row_stride,
                                                 int n_seqs, int max_new, int Hq, int Hkv, int hd, const void* k_cache,
                                                 const void* v_cache, int n_pages, const int* seq_start,
                                                 const int* seq_len_after, const int* block_table, int bt_stride,
-                                                int window, int chunk, float scale, float softcap, void* stream) {
+                                                int window, int chunk, float scale, float softcap, const float* sink,
+                                                void* stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0 || chunk < 0 || scale < 0.f || softcap < 0.f) return ODIN_ERR_BAD_ARG;
     if ((q_row_stride % 8) || (((uintptr_t)q) & 15) || (out_row_stride % 8) || (((uintptr_t)out) & 15))
@@ -538,6 +543,7 @@ extern "C" int odin_attention_prefill_tc_masked(const void* q, long long q_row_s
     p.chunk = chunk;
     p.scale_log2 = 1.4426950408889634f * (scale > 0.f ? scale : 1.0f / sqrtf((float)hd));
     p.cap_log2 = softcap > 0.f ? 1.4426950408889634f * softcap : 0.f;
+    p.sink = sink;
     p.error = tc_error_flag();
     cudaStream_t s = (cudaStream_t)stream;
     const bool extra = chunk > 0 || softcap > 0.f;
@@ -553,7 +559,7 @@ extern "C" int odin_attention_prefill_tc(const void* q, long long q_row_stride, 
                                          void* stream) {
     return odin_attention_prefill_tc_masked(q, q_row_stride, out, out_row_stride, n_seqs, max_new, Hq, Hkv, hd, k_cache,
                                             v_cache, n_pages, seq_start, seq_len_after, block_table, bt_stride, window,
-                                            0, 0.f, 0.f, stream);
+                                            0, 0.f, 0.f, nullptr, stream);
 }
 
 #ifdef ODIN_TRACE

@@ -57,6 +57,7 @@ struct GemmParams {
     int stages;            // length of the ring of stages (0: as many as fit)
     int staged;            // mode 1: K blocks of a CTA's first item whose weights wait in tensor memory (see the kernel)
     int* error;            // set when a wait runs out
+    int gate_act = 0;      // DUAL: what the gate goes through, 0 SiLU, 1 tanh-GELU
 };
 
 // DUAL: two Y tiles per stage (rows [j, j+BN) and [dual_offset + j, dual_offset + j + BN) of Y) and
@@ -396,11 +397,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     tc::tmem_ld32(taddr, r);
                     tc::tmem_ld32(taddr + BN, u);
                     tc::tmem_ld_wait();
+                    if (p.gate_act == 0) {
 #pragma unroll
-                    for (int q = 0; q < 32; ++q) {
-                        float g = __uint_as_float(r[q]);
-                        g = __fdividef(g, 1.0f + __expf(-g));  // one ex2 and one rcp: the epilogue's arithmetic is not free beside the MMAs
-                        r[q] = __float_as_uint(g * __uint_as_float(u[q]));
+                        for (int q = 0; q < 32; ++q) {
+                            float g = __uint_as_float(r[q]);
+                            g = __fdividef(g, 1.0f + __expf(-g));  // one ex2 and one rcp: the epilogue's arithmetic is not free beside the MMAs
+                            r[q] = __float_as_uint(g * __uint_as_float(u[q]));
+                        }
+                    } else {
+                        // tanh-GELU: g (1 + tanh(y)) / 2 = g sigmoid(2 y), y = sqrt(2 / pi) (g + 0.044715 g^3)
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) {
+                            float g = __uint_as_float(r[q]);
+                            const float y2 = 1.5957691216057308f * g * fmaf(0.044715f * g, g, 1.0f);
+                            g = __fdividef(g, 1.0f + __expf(-y2));
+                            r[q] = __float_as_uint(g * __uint_as_float(u[q]));
+                        }
                     }
                 } else if (CH == 32) {
                     tc::tmem_ld32(taddr, r);
@@ -722,9 +734,17 @@ extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
 // C[M, I] = silu(A Wg^T) * (A Wu^T) for W = [Wg; Wu] of shape [2 I, K]: the gate and up products
 // accumulate side by side in tensor memory and the SwiGLU is applied as they are read back, so
 // the [M, 2 I] intermediate never exists.  For many tokens (mode 0, tiles of 128 output columns).
+// odin_gemm_tc_gated: the same with the gate's activation chosen, 0 SiLU, 1 tanh-GELU.
+extern "C" int odin_gemm_tc_gated(const void* A, const void* W, void* C, int c_dtype, int M, int I, int K,
+                                  long long lda, long long ldw, long long ldc, int act, void* stream);
 extern "C" int odin_gemm_tc_swiglu(const void* A, const void* W, void* C, int c_dtype, int M, int I, int K,
                                    long long lda, long long ldw, long long ldc, void* stream) {
+    return odin_gemm_tc_gated(A, W, C, c_dtype, M, I, K, lda, ldw, ldc, 0, stream);
+}
+extern "C" int odin_gemm_tc_gated(const void* A, const void* W, void* C, int c_dtype, int M, int I, int K,
+                                  long long lda, long long ldw, long long ldc, int act, void* stream) {
     if (M <= 0 || I <= 0) return 0;
+    if (act != 0 && act != 1) return ODIN_ERR_BAD_ARG;
     if (K <= 0) return ODIN_ERR_BAD_ARG;
     if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
     constexpr int BN = 128;
@@ -739,6 +759,7 @@ extern "C" int odin_gemm_tc_swiglu(const void* A, const void* W, void* C, int c_
     p.stages = 0;
     p.staged = 0;
     p.dual_offset = I;
+    p.gate_act = act;
     p.error = error_flag();
     p.rows_x = M;
     p.rows_y = I;

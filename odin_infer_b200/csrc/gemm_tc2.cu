@@ -58,6 +58,7 @@ struct Params2 {
     // parts, part s written to the slice s of the output, split_stride elements apart, as C[token][weight row].
     int n_split, kb_per_split;
     long long split_stride;
+    int gate_act = 0;      // DUAL: what the gate goes through, 0 SiLU, 1 tanh-GELU
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -330,11 +331,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tc::tmem_ld32(taddr, r);
                     tc::tmem_ld32(taddr + BN / 4, u);
                     tc::tmem_ld_wait();
+                    if (p.gate_act == 0) {
 #pragma unroll
-                    for (int q = 0; q < 32; ++q) {
-                        float g = __uint_as_float(r[q]);
-                        g = __fdividef(g, 1.0f + __expf(-g));  // one ex2 and one rcp: the epilogue's arithmetic is not free beside the MMAs
-                        r[q] = __float_as_uint(g * __uint_as_float(u[q]));
+                        for (int q = 0; q < 32; ++q) {
+                            float g = __uint_as_float(r[q]);
+                            g = __fdividef(g, 1.0f + __expf(-g));  // one ex2 and one rcp: the epilogue's arithmetic is not free beside the MMAs
+                            r[q] = __float_as_uint(g * __uint_as_float(u[q]));
+                        }
+                    } else {
+                        // tanh-GELU: g (1 + tanh(y)) / 2 = g sigmoid(2 y), y = sqrt(2 / pi) (g + 0.044715 g^3)
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) {
+                            float g = __uint_as_float(r[q]);
+                            const float y2 = 1.5957691216057308f * g * fmaf(0.044715f * g, g, 1.0f);
+                            g = __fdividef(g, 1.0f + __expf(-y2));
+                            r[q] = __float_as_uint(g * __uint_as_float(u[q]));
+                        }
                     }
                 } else {
                     tc::tmem_ld32(taddr, r);
@@ -496,9 +508,17 @@ extern "C" int odin_gemm_tc2(const void* A, const void* W, void* C, int c_dtype,
 
 // C[M, I] = silu(A Wg^T) * (A Wu^T) for W = [Wg; Wu] of shape [2 I, K], on pairs of SMs (tiles of 256 rows
 // and 128 output columns: the gate and up products side by side in tensor memory).
+// odin_gemm_tc2_gated: the same with the gate's activation chosen, 0 SiLU, 1 tanh-GELU.
+extern "C" int odin_gemm_tc2_gated(const void* A, const void* W, void* C, int c_dtype, int M, int I, int K,
+                                   long long lda, long long ldw, long long ldc, int act, void* stream);
 extern "C" int odin_gemm_tc2_swiglu(const void* A, const void* W, void* C, int c_dtype, int M, int I, int K,
                                     long long lda, long long ldw, long long ldc, void* stream) {
+    return odin_gemm_tc2_gated(A, W, C, c_dtype, M, I, K, lda, ldw, ldc, 0, stream);
+}
+extern "C" int odin_gemm_tc2_gated(const void* A, const void* W, void* C, int c_dtype, int M, int I, int K,
+                                   long long lda, long long ldw, long long ldc, int act, void* stream) {
     if (M <= 0 || I <= 0) return 0;
+    if (act != 0 && act != 1) return ODIN_ERR_BAD_ARG;
     if (K <= 0) return ODIN_ERR_BAD_ARG;
     if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
     // a box of 64 weight rows must not run from the gate half into the up half
@@ -509,6 +529,7 @@ extern "C" int odin_gemm_tc2_swiglu(const void* A, const void* W, void* C, int c
     p.tiles_n = (I + BN / 2 - 1) / (BN / 2);
     p.kb_total = (K + BK - 1) / BK;
     p.dual_offset = I;
+    p.gate_act = act;
     p.n_split = 1; p.kb_per_split = p.kb_total; p.split_stride = 0;
     p.accumulate = 0;
     p.error = error_flag2();

@@ -456,17 +456,21 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
         c_longlong(stride), c_int(stages), c_int(staged), _stream()), "gemm_tc")
 
 
-def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, I] = silu(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu] ([2 I, K]) in one tcgen05 kernel."""
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1}   # what the gate of a gated product's epilogue goes through
+
+
+def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[M, I] = act(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu] ([2 I, K]) in one tcgen05 kernel; act: silu
+    (SwiGLU) or gelu_tanh (GeGLU)."""
     M, K = a.shape
     I = out.shape[1]
     if not gemm_tc_supported(a, w_gate_up):
         raise KernelError("gemm_tc_swiglu: operands must be bfloat16 with 16-byte aligned rows")
     assert w_gate_up.shape == (2 * I, K) and out.shape[0] == M and out.stride(1) == 1
-    _check(_fn("gemm_tc", "odin_gemm_tc_swiglu")(
+    _check(_fn("gemm_tc", "odin_gemm_tc_gated")(
         _ptr(a), _ptr(w_gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
-        c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)), _stream()),
-        "gemm_tc_swiglu")
+        c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)),
+        c_int(GATE_ACTS[activation]), _stream()), "gemm_tc_swiglu")
 
 
 def gemm_tc2(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
@@ -509,17 +513,18 @@ def gemm_tc2_swiglu_supported(inner: int) -> bool:
     return inner % 64 == 0
 
 
-def gemm_tc2_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, I] = silu(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu] ([2 I, K]) on pairs of SMs; I a multiple of 64."""
+def gemm_tc2_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[M, I] = act(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu] ([2 I, K]) on pairs of SMs; I a multiple of 64;
+    act: silu or gelu_tanh."""
     M, K = a.shape
     I = out.shape[1]
     if not gemm_tc_supported(a, w_gate_up):
         raise KernelError("gemm_tc2_swiglu: operands must be bfloat16 with 16-byte aligned rows")
     assert w_gate_up.shape == (2 * I, K) and out.shape[0] == M and out.stride(1) == 1
-    _check(_fn("gemm_tc", "odin_gemm_tc2_swiglu")(
+    _check(_fn("gemm_tc", "odin_gemm_tc2_gated")(
         _ptr(a), _ptr(w_gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
-        c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)), _stream()),
-        "gemm_tc2_swiglu")
+        c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)),
+        c_int(GATE_ACTS[activation]), _stream()), "gemm_tc2_swiglu")
 
 
 def gemm_tc_check() -> None:
@@ -635,9 +640,9 @@ def attention_decode_scratch(n_tokens: int, n_q: int, head_dim: int, n_split: in
 def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                      k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
                      block_table: torch.Tensor, window: int, scratch: torch.Tensor, n_split: int, chunk: int = 0,
-                     scale: float = 0.0, softcap: float = 0.0) -> None:
+                     scale: float = 0.0, softcap: float = 0.0, sink: torch.Tensor | None = None) -> None:
     """One query token per row over its sequence's bfloat16 cache, keys split n_split ways.
-    chunk, scale, softcap: as `attention_plain` takes them.
+    chunk, scale, softcap, sink: as `attention_plain` takes them.
 
     The counters on which a launch's key splits meet are one array of the library: all
     decode-attention launches of a process must be ordered on the GPU (one stream, or events
@@ -652,7 +657,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, he
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE), c_int(k_cache.shape[0]), _ptr(tok_pos),
         _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window), c_int(chunk), c_float(scale),
-        c_float(softcap), _ptr(scratch), c_int(n_split), _stream()), "attention_decode", kernels=1 if head_dim in (64, 128) and n_q // n_kv <= 16 else 2)
+        c_float(softcap), _ptr(_sink(sink, n_q)), _ptr(scratch), c_int(n_split), _stream()), "attention_decode", kernels=1 if head_dim in (64, 128) and n_q // n_kv <= 16 else 2)
 
 
 def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
@@ -710,7 +715,7 @@ def attention_prefill_supported(head_dim: int) -> bool:
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_q: int, n_kv: int,
                       head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_start: torch.Tensor,
                       seq_len_after: torch.Tensor, block_table: torch.Tensor, window: int = 0, chunk: int = 0,
-                      scale: float = 0.0, softcap: float = 0.0) -> None:
+                      scale: float = 0.0, softcap: float = 0.0, sink: torch.Tensor | None = None) -> None:
     """Flash attention of each sequence's new tokens (rows seq_start[b]..seq_start[b+1] of q) over its
     bfloat16 cache, which already holds this step's keys and values: tcgen05.mma with accumulators in
     tensor memory."""
@@ -723,7 +728,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: 
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(n_seqs), c_int(max_new),
         c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(k_cache.shape[0]),
         _ptr(seq_start), _ptr(seq_len_after), _ptr(block_table), c_int(block_table.stride(0)), c_int(window),
-        c_int(chunk), c_float(scale), c_float(softcap), _stream()), "attention_prefill")
+        c_int(chunk), c_float(scale), c_float(softcap), _ptr(_sink(sink, n_q)), _stream()), "attention_prefill")
 
 
 def attention_prefill_check() -> None:

@@ -198,22 +198,22 @@ class Runtime:
     def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, inner: int, activation: str = "silu") -> torch.Tensor:
         """silu(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu]: one kernel with the SwiGLU in its
         epilogue for many bfloat16 tokens, else the product followed by the SwiGLU kernel
-        (which also adds the partial sums of a split product).  Another activation of the gate
-        (gelu_tanh) runs as the product followed by the gated-activation kernel."""
+        (which also adds the partial sums of a split product).  activation: what the gate goes through,
+        silu or gelu_tanh; the epilogues know both, the row kernel for the other is the gated-activation kernel."""
         M = a.shape[0]
         act = self.empty(M, inner)
-        if activation != "silu":
-            ops.gated_activation(self.linear(a, w_gate_up, out_dtype=torch.float32, may_split=True), activation, act)
-            return act
         # From 129 tokens on the pair kernel with the SwiGLU in its epilogue: the gate|up weight has tiles
         # enough for the pairs of SMs even beside one tile of 256 tokens, and no partial sums are written
         # (measured against the weights-wide kernel + SwiGLU kernel: 8 to 10 % of the step at 129 to 256 tokens).
         fused_from = SWIGLU_FUSED_FROM
         if M >= fused_from and ops.gemm_tc_supported(a, w_gate_up):
             if M > 128 and ops.gemm_tc2_swiglu_supported(inner):
-                ops.gemm_tc2_swiglu(a, w_gate_up, act)
+                ops.gemm_tc2_swiglu(a, w_gate_up, act, activation)
             else:
-                ops.gemm_tc_swiglu(a, w_gate_up, act)
+                ops.gemm_tc_swiglu(a, w_gate_up, act, activation)
+            return act
+        if activation != "silu":
+            ops.gated_activation(self.linear(a, w_gate_up, may_split=True), activation, act)
             return act
         ops.swiglu(self.linear(a, w_gate_up, may_split=True), act)
         return act
@@ -271,18 +271,16 @@ class Runtime:
         the scores; every kernel takes them.  sink: float32 [n_q], a logit per head that joins the softmax's
         denominator."""
         same_heads = (v_head_dim or head_dim) == head_dim   # the fast kernels' value heads have the keys' size
-        if sink is not None:
-            same_heads = False
         if self.dtype == torch.bfloat16 and same_heads and step.all_single and ops.attention_decode_supported(head_dim):
             B = q.shape[0]
             n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms)
             scratch = self.empty(ops.attention_decode_scratch(B, n_q, head_dim, n_split), dtype=torch.float32)
             ops.attention_decode(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
-                                 window, scratch, n_split, chunk, scale, softcap)
+                                 window, scratch, n_split, chunk, scale, softcap, sink)
             return
         if self.dtype == torch.bfloat16 and same_heads and not step.all_single and ops.attention_prefill_supported(head_dim):
             ops.attention_prefill(q, out, step.n_seq_cap, step.max_new, n_q, n_kv, head_dim, k_line, v_line,
-                                  step.seq_start, step.seq_len_after, block_table, window, chunk, scale, softcap)
+                                  step.seq_start, step.seq_len_after, block_table, window, chunk, scale, softcap, sink)
             return
         ops.attention_plain(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
                             window, chunk, scale, softcap, v_head_dim, sink)

@@ -16,14 +16,16 @@ class RotaryEncoding(PositionEncoding):
 
     stretch = {"factor", "low", "high", "original"}: frequencies are stretched by their wavelength
     l = 2 pi / f: kept where l < original / high, divided by `factor` where l > original / low, and
-    between the two blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    between the two blended, (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+    precise (always so with a stretch): the frequencies are formed in double and rounded to 32-bit once, instead of
+    by the reference's 32-bit power."""
 
     graph_safe = True
 
-    def __init__(self, rotary_dim: int, theta: float, stretch: dict | None = None):
+    def __init__(self, rotary_dim: int, theta: float, stretch: dict | None = None, precise: bool = False):
         if rotary_dim % 2:
             raise ValueError(f"rotary_dim must be even, got {rotary_dim}")
-        self.rotary_dim, self.theta = rotary_dim, float(theta)
+        self.rotary_dim, self.theta, self.precise = rotary_dim, float(theta), bool(precise)
         self.stretch = None
         if stretch is not None:
             self.stretch = {k: float(stretch[k]) for k in ("factor", "low", "high", "original")}
@@ -35,10 +37,12 @@ class RotaryEncoding(PositionEncoding):
         """The rotary_dim / 2 frequencies as 32-bit floats."""
         half = self.rotary_dim // 2
         i = np.arange(half, dtype=np.float32)
-        if self.stretch is None:
+        if self.stretch is None and not self.precise:
             return (np.float32(1.0) / np.power(np.float32(self.theta), i / np.float32(max(half, 1)))).astype(np.float32)
-        st = self.stretch
         f = np.power(np.float64(self.theta), -np.arange(half, dtype=np.float64) / max(half, 1))
+        if self.stretch is None:
+            return f.astype(np.float32)
+        st = self.stretch
         wavelength = 2.0 * np.pi / f
         s = (st["original"] / wavelength - st["low"]) / (st["high"] - st["low"])
         blended = (1.0 - s) * f / st["factor"] + s * f

@@ -94,19 +94,23 @@ def window_sink_attention(q, k, v, scale: float, window: int, sink: torch.Tensor
 
 def attention_mixer(h: torch.Tensor, w: dict, p: str, mx: dict, eps: float, kind: str) -> torch.Tensor:
     n = h.shape[0]
-    H, G, dk, dv = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"]
+    H, dk = mx["heads"], mx["dim"]
+    G, dv = mx.get("kv_heads", H), mx.get("vdim", dk)       # absent: as many key heads as query heads, values as wide as keys
+    window = int(mx["mask"]["size"]) if mx.get("mask") else n   # absent: every earlier key
+    scale = float(mx.get("scale", dk ** -0.5))
     q = (h @ w[p + "q"].T).reshape(n, H, dk)
     k = (h @ w[p + "k"].T).reshape(n, G, dk)
     v = (h @ w[p + "v"].T).reshape(n, G, dv)
     if kind == "attention_2":
         q = plain_norm(q, w[p + "q.norm"], eps)
         k = plain_norm(k, w[p + "k.norm"], eps)
-        rot = mx["rot"]
-        freqs = stretched_frequencies(rot["dims"], float(rot["base"]), rot.get("scaling"))
-        pos = torch.arange(n)
-        q = rotate_half(q, pos, freqs, rot["dims"])
-        k = rotate_half(k, pos, freqs, rot["dims"])
-    o = window_sink_attention(q, k, v, float(mx["scale"]), int(mx["mask"]["size"]), w[p + "sink"])
+        rot = mx.get("rot")
+        if rot is not None:
+            freqs = stretched_frequencies(rot["dims"], float(rot["base"]), rot.get("scaling"))
+            pos = torch.arange(n)
+            q = rotate_half(q, pos, freqs, rot["dims"])
+            k = rotate_half(k, pos, freqs, rot["dims"])
+    o = window_sink_attention(q, k, v, scale, window, w[p + "sink"])
     gate = torch.sigmoid(h @ w[p + "g"].T)
     if kind == "attention_2":
         o = o * gate[:, :, None]                # one number per head
@@ -143,7 +147,7 @@ def forward(config: dict, weights: dict, tokens, return_layers: bool = False):
     every entry of `layers`, [entries, n, width]."""
     w = {k: v.to(F64) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
-    x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float(config["embedding"]["scale"])
+    x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float((config.get("embedding") or {}).get("scale", 1.0))
     stream = []
     for i, layer in enumerate(config["layers"]):
         src = layer.get("weights_of", i)
