@@ -485,6 +485,197 @@ def tovalix_workload(steps: int, warmup: int) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------------------------------------------
+# --workload nufupel: the Nufupel design beside the Qwen3 dense decoder at equal sizes
+# --------------------------------------------------------------------------------------------------------------
+NUFUPEL_SIZES = {
+    # width, heads / kv heads / head size, experts x inner (top of them per token) beside a shared expert; the dense
+    # layers' and the Qwen3 decoder's inner size is what a token uses of an expert layer (top x inner + shared)
+    "2048": dict(width=2048, heads=16, kv=8, hd=128, experts=32, top=4, eff=768, shared=1536, layers=8, vocab=32768,
+                 window=1024),
+    "4096": dict(width=4096, heads=32, kv=8, hd=128, experts=64, top=6, eff=1024, shared=2048, layers=4, vocab=32768,
+                 window=1024),
+}
+
+
+def nufupel_config(z: dict) -> dict:
+    ff = z["top"] * z["eff"] + z["shared"]
+    base = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5,
+            "mask": {"size": z["window"]}}
+    rot = {"dims": z["hd"] // 2, "base": 250000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared"]}}
+    layers = []
+    for i in range(z["layers"]):
+        if i % 4 == 0:
+            layers.append({"type": "attention_2", "mixer": dict(base, rot=rot), "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe})
+        elif i % 4 == 1:
+            layers.append({"type": "attention", "mixer": dict(base, mask={"size": z["window"] // 2}), "mlp": moe})
+        else:
+            layers.append(dict(layers[i - i % 4 + 1], weights_of=i - i % 4 + 1))
+    return {"architecture": "Nufupel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(z["width"]) ** 0.5}, "logit_softcap": 30.0, "layers": layers}
+
+
+def nufupel_kernels(z: dict, T: int, peaks: dict) -> dict:
+    """Every kernel that the design adds, alone at this size for T token rows, beside the like kernel of the Qwen3
+    decoder: microseconds, and algorithmic bytes (or FLOPs) over the time as a fraction of the measured peaks."""
+    import torch
+    from odin_infer_b200.csrc import ops
+    from odin_infer_b200.engine import runtime as R
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    d, hd, Hq, Hkv = z["width"], z["hd"], z["heads"], z["kv"]
+    E, top, eff = z["experts"], z["top"], z["eff"]
+    always = z["shared"] // eff
+    ff = top * eff + z["shared"]
+    decode = T <= 64
+    out = {}
+
+    def replayed(fn, flush, reps=5, inner=20):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        return _timed(graph.replay, flush, reps) / inner
+    timed = replayed if decode else _timed
+
+    def note(name, us, nbytes=None, flops=None):
+        e = {"us": round(us, 2)}
+        if nbytes is not None:
+            e["of_hbm"] = round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            e["tflops"] = round(flops / (us * 1e-6) / 1e12, 1)
+            e["of_bf16"] = round(flops / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 3)
+        out[name] = e
+    rt = R.Runtime(dev, bf)
+    torch.manual_seed(0)
+    h = torch.randn(T, d, device=dev).to(bf)
+    x = torch.randn(T, d, device=dev)
+    w1 = torch.randn(d, device=dev)
+    hb = torch.empty(T, d, dtype=bf, device=dev)
+    # norm: one update against three
+    d1 = torch.randn(2, T, d, device=dev)
+    d2 = torch.randn(T, d, device=dev)
+    note("add_rmsnorm (qwen3)", timed(lambda: ops.add_rmsnorm(x, d1, w1, 1e-6, hb), flush), nbytes=T * d * (4 * 4 + 2))
+    note("add_rmsnorm, three updates", timed(lambda: ops.row_update(x, [d1, d2, d1], None, w1, 1e-6, 1, hb), flush),
+         nbytes=T * d * (4 * 7 + 2))
+    # gate on the heads, gated activations
+    o = torch.randn(T, Hq * hd, device=dev).to(bf)
+    wide = torch.randn(2 if decode else 1, T, (Hq + 2 * Hkv) * hd + Hq * hd, device=dev)
+    if not decode:
+        wide = wide[0].to(bf)
+    g0 = (Hq + 2 * Hkv) * hd
+    note("sigmoid gate per element", timed(lambda: ops.sigmoid_gate(o, wide[..., g0:], Hq, hd, False), flush),
+         nbytes=T * Hq * hd * (4 + wide.element_size() * (wide.shape[0] if wide.dim() == 3 else 1)))
+    note("sigmoid gate per head", timed(lambda: ops.sigmoid_gate(o, wide[..., g0:g0 + Hq], Hq, hd, True), flush), nbytes=T * Hq * hd * 4)
+    gu = torch.randn(2, T, 2 * ff, device=dev) if decode else torch.randn(T, 2 * ff, device=dev).to(bf)
+    act = torch.empty(T, ff, dtype=bf, device=dev)
+    nb = gu.numel() * gu.element_size() + act.numel() * 2
+    note("swiglu (qwen3)", timed(lambda: ops.swiglu(gu, act), flush), nbytes=nb)
+    note("geglu", timed(lambda: ops.gated_activation(gu, "gelu_tanh", act), flush), nbytes=nb)
+    # gate|up with the activation in the epilogue
+    if not decode:
+        wgu = (torch.randn(2 * ff, d, device=dev) * 0.02).to(bf)
+        fl = 2.0 * T * 2 * ff * d
+        note("gate|up product + swiglu epilogue (qwen3)", timed(lambda: ops.gemm_tc2_swiglu(h, wgu, act, "silu"), flush), flops=fl)
+        note("gate|up product + geglu epilogue", timed(lambda: ops.gemm_tc2_swiglu(h, wgu, act, "gelu_tanh"), flush), flops=fl)
+    # router and experts
+    wr = (torch.randn(E, d, device=dev) / d ** 0.5).to(bf)
+    ids = torch.empty(T, top + always, dtype=torch.int32, device=dev)
+    wts = torch.empty(T, top + always, dtype=torch.float32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    note("router (logits, choice, weights)", timed(lambda: ops.moe_router(h, wr, None, top, always, seq, ids, wts), flush),
+         nbytes=T * d * 2 + E * d * 2)
+    n_e = E + always
+    wg = (torch.randn(n_e, 2 * eff, d, device=dev) * 0.02).to(bf)
+    wd = (torch.randn(n_e, d, eff, device=dev) * 0.02).to(bf)
+    used = len(torch.unique(ids))
+    fl = 2.0 * T * (top + always) * 3 * eff * d
+    note("experts (all their launches)", timed(lambda: rt.experts(h, wg, wd, ids, wts, "silu"), flush), flops=fl,
+         nbytes=used * 3 * eff * d * 2)
+    out["experts (all their launches)"]["experts_used"] = used
+    # the dense feed-forward of what a token uses of the experts, as the Qwen3 decoder runs it
+    wgu = (torch.randn(2 * ff, d, device=dev) * 0.02).to(bf)
+    wdn = (torch.randn(d, ff, device=dev) * 0.02).to(bf)
+    note("dense feed-forward of equal active size (qwen3)",
+         timed(lambda: rt.linear(rt.gated_linear(h, wgu, ff), wdn, out_dtype=torch.float32, may_split=True), flush),
+         flops=2.0 * T * 3 * ff * d, nbytes=3 * ff * d * 2)
+    # attention with and without the sink
+    ctx = T if not decode else 512
+    n_pages = (ctx + 63) // 64 * (1 if not decode else T) + 2
+    kc = (torch.randn(n_pages, Hkv, 64, hd, device=dev) * 0.3).to(bf)
+    vc = (torch.randn(n_pages, Hkv, 64, hd, device=dev) * 0.3).to(bf)
+    q = (torch.randn(T, Hq * hd, device=dev) * 0.3).to(bf)
+    ao = torch.empty(T, Hq * hd, dtype=bf, device=dev)
+    sink = torch.randn(Hq, device=dev)
+    if decode:
+        per_seq = (ctx + 63) // 64
+        bt = torch.arange(T * per_seq, dtype=torch.int32, device=dev).reshape(T, per_seq).contiguous()
+        pos = torch.full((T,), ctx - 1, dtype=torch.int32, device=dev)
+        sq = torch.arange(T, dtype=torch.int32, device=dev)
+        n_split = R.decode_key_splits(T, Hkv, ctx)
+        scratch = torch.empty(ops.attention_decode_scratch(T, Hq, hd, n_split), dtype=torch.float32, device=dev)
+        nb = T * ctx * Hkv * hd * 2 * 2
+        for name, sk in (("decode attention (qwen3)", None), ("decode attention with a sink", sink)):
+            note(name, timed(lambda: ops.attention_decode(q, ao, Hq, Hkv, hd, kc, vc, pos, sq, bt, 0, scratch, n_split, 0, hd ** -0.5, 0.0, sk), flush), nbytes=nb)
+    else:
+        bt = torch.arange((ctx + 63) // 64, dtype=torch.int32, device=dev).reshape(1, -1).contiguous()
+        starts = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        lens = torch.tensor([T], dtype=torch.int32, device=dev)
+        fl = 4.0 * Hq * hd * (T * (T + 1) // 2)
+        w = z["window"]
+        inside = 4.0 * Hq * hd * (w * (w + 1) // 2 + (T - w) * w) if T > w else fl
+        note("prompt attention (qwen3)", timed(lambda: ops.attention_prefill(q, ao, 1, T, Hq, Hkv, hd, kc, vc, starts, lens, bt, 0, 0, hd ** -0.5, 0.0), flush), flops=fl)
+        note("prompt attention with a sink", timed(lambda: ops.attention_prefill(q, ao, 1, T, Hq, Hkv, hd, kc, vc, starts, lens, bt, 0, 0, hd ** -0.5, 0.0, sink), flush), flops=fl)
+        note("prompt attention with a sink and the window", timed(lambda: ops.attention_prefill(q, ao, 1, T, Hq, Hkv, hd, kc, vc, starts, lens, bt, w, 0, hd ** -0.5, 0.0, sink), flush), flops=inside)
+    torch.cuda.synchronize()
+    ops.attention_prefill_check()
+    ops.attention_decode_check()
+    ops.moe_tc_check()
+    return out
+
+
+def nufupel_workload(steps: int, warmup: int) -> int:
+    """The Nufupel design at two sizes that resemble a real model's layers, beside the Qwen3 dense decoder of the same
+    width, attention heads, number of layers and vocabulary, whose feed-forward has the size that a token uses of an
+    expert layer (random weights): a prompt of 2,048 tokens in one step, decoding at batch 8 after 512-token prompts
+    (device-timed), and every new kernel alone."""
+    import torch
+    from odin_infer_b200 import Engine, Engine_Opts
+    from odin_infer_b200.config import config_from_dict
+    from odin_infer_b200.csrc import ops
+    peaks, peak_source = load_peaks()
+    result = {"metric": "Nufupel beside the Qwen3 dense decoder at equal sizes: prompt of 2,048 tokens, decode at batch 8 "
+                        "(512-token prompts), bf16, random weights", "peak_source": peak_source, "sizes": {}}
+    steps = min(steps, 64)
+    for name, z in NUFUPEL_SIZES.items():
+        entry = {}
+        ff = z["top"] * z["eff"] + z["shared"]
+        like = dict(z, ff=ff)
+        for model, raw in (("nufupel", nufupel_config(z)), ("qwen3", qwen3_config_like(like))):
+            need = PROMPT + warmup + steps + 72
+            engine = Engine.random(config_from_dict(raw), WEIGHT_SEED, Engine_Opts(
+                max_ctx=CONTEXT, max_tokens=max(8 * ((need + 63) // 64 * 64), PREFILL_TOKENS + 64), max_batch=8,
+                dtype="bfloat16", verbose=False))
+            ms_pf = run_prefill(engine, z["vocab"])
+            tps, ms_step, _, launches = run_decode(engine, 8, steps, warmup, z["vocab"])
+            entry[model] = {"layers": z["layers"], "weights_gib": round(engine.weight_bytes / 2 ** 30, 2),
+                            "prefill_2048": {"ms": round(ms_pf, 3), "tokens_per_s": round(PREFILL_TOKENS / ms_pf * 1e3)},
+                            "decode_b8": {"ms_per_step": round(ms_step, 4), "tokens_per_s": round(tps, 1),
+                                          "launches_per_step": launches // steps}}
+            engine.destroy()
+            del engine
+            torch.cuda.empty_cache()
+        entry["kernels_prompt_2048_rows"] = nufupel_kernels(z, PREFILL_TOKENS, peaks)
+        entry["kernels_decode_8_rows"] = nufupel_kernels(z, 8, peaks)
+        result["sizes"][name] = entry
+    ops.gemm_tc_check()
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -496,11 +687,12 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for profilers)")
-    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long", "tovalix"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long", "tovalix", "nufupel"],
                     help="8b: the contract's run (default).  The others are further workloads of the baseline's list and "
                          "print a line of their own: 1.7b-mixed = Qwen3-1.7B shape, 64 prompts of 16..2048 tokens, 128 new "
                          "tokens each; 32b-long = Qwen3-32B shape, a 2,048-token prompt, decoding 1 and 8 sequences at context 8192; "
-                         "tovalix = the Tovalix design beside the Qwen3 decoder at equal sizes, and its kernels alone")
+                         "tovalix = the Tovalix design beside the Qwen3 decoder at equal sizes, and its kernels alone; "
+                         "nufupel = the same for the Nufupel design")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -514,6 +706,8 @@ def main() -> int:
     warmup = max(args.warmup, 3)
     if args.workload == "tovalix":
         return tovalix_workload(args.steps, warmup)
+    if args.workload == "nufupel":
+        return nufupel_workload(args.steps, warmup)
     if args.workload != "8b":
         return other_workload(args.workload)
 

@@ -30,6 +30,7 @@ GROUPS = {
     "rowwise": ["rowwise.cu"],
     "recurrent": ["recurrent.cu"],
     "moe": ["moe.cu"],
+    "moe_tc": ["moe_tc.cu"],
     "gemm_plain": ["gemm_plain.cu"],
     "head_prep": ["head_prep.cu"],
     "attention_plain": ["attention_plain.cu"],

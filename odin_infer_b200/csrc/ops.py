@@ -310,6 +310,73 @@ def moe_down(a: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, wts: torch.Ten
         c_int(per), c_int(ff), c_int(d), _ptr(out), _stream()), "moe_down")
 
 
+def moe_places(rows: int, n_experts: int) -> int:
+    """Places that `rows` rows take at most once every expert's rows are padded to whole tiles of 128."""
+    return (rows + n_experts * 127 + 127) // 128 * 128
+
+
+def moe_grouped_supported(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> bool:
+    """Shapes and types that the grouped tensor-core products take (bfloat16, rows of whole 16 bytes)."""
+    d, inner = w_gate_up.shape[2], w_down.shape[2]
+    return (h.dtype == w_gate_up.dtype == w_down.dtype == torch.bfloat16 and d % 8 == 0 and inner % 8 == 0
+            and h.stride(1) == 1 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0)
+
+
+def moe_plan(ids: torch.Tensor, n_experts: int, place_of_row: torch.Tensor, row_of_place: torch.Tensor,
+             tile_expert: torch.Tensor) -> None:
+    """The rows (token, choice) of ids [T, per] in the order of their experts, every expert's rows padded to whole
+    tiles of 128 places: place_of_row [T * per] (-1: the row has no expert), row_of_place [places] (-1: padding),
+    tile_expert [places / 128] (-1: a tile that no rows reach).  Which place a row gets among its expert's is not
+    fixed; nothing that is computed from a row depends on it."""
+    rows = ids.numel()
+    assert ids.dtype == torch.int32 and ids.is_contiguous() and place_of_row.numel() == rows
+    assert row_of_place.numel() >= moe_places(rows, n_experts) and tile_expert.numel() * 128 == row_of_place.numel()
+    _check(_fn("moe_tc", "odin_moe_plan")(_ptr(ids), c_int(rows), c_int(n_experts), _ptr(place_of_row), _ptr(row_of_place),
+                                          c_int(row_of_place.numel()), _ptr(tile_expert), _stream()), "moe_plan")
+
+
+def moe_gather(h: torch.Tensor, row_of_place: torch.Tensor, per: int, out: torch.Tensor) -> None:
+    """out[place] = h[row_of_place[place] // per] (bfloat16), zeros where the place is padding."""
+    assert h.dtype == out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (row_of_place.numel(), h.shape[1])
+    _check(_fn("moe_tc", "odin_moe_gather")(_ptr(h), c_longlong(h.stride(0)), _ptr(row_of_place), c_int(out.shape[0]),
+                                            c_int(per), c_int(h.shape[1]), _ptr(out), _stream()), "moe_gather")
+
+
+def moe_grouped(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor, kind: str | None = None) -> None:
+    """Every tile of 128 sorted rows of a [places, K] times the matrix of the tile's own expert (tcgen05).
+    kind None: w [experts, N, K], out float32 [places, N] = a W[e]^T.  kind silu / gelu_tanh: w [experts, 2 N, K]
+    (gate rows first), out bfloat16 [places, N] = act(a Wg[e]^T) * (a Wu[e]^T)."""
+    places, K = a.shape
+    n_e, rpe = w.shape[0], w.shape[1]
+    N = out.shape[1]
+    dual = kind is not None
+    assert a.dtype == w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous() and w.shape[2] == K
+    assert out.is_contiguous() and out.shape[0] == places and out.dtype == (torch.bfloat16 if dual else torch.float32)
+    assert tile_expert.numel() * 128 == places and rpe == (2 * N if dual else N)
+    _check(_fn("moe_tc", "odin_moe_grouped")(
+        _ptr(a), c_longlong(a.stride(0)), _ptr(w), c_longlong(K), c_int(n_e), c_int(rpe), c_int(places), c_int(N), c_int(K),
+        c_int(1 if dual else 0), c_int(ACTIVATIONS[kind] if dual else 0), _ptr(tile_expert), _ptr(out),
+        c_longlong(out.stride(0)), _stream()), "moe_grouped")
+
+
+def moe_combine(c: torch.Tensor, place_of_row: torch.Tensor, wts: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = sum_k wts[t, k] * c[place_of_row[t * per + k]] (float32), the choices in their order."""
+    T, per = wts.shape
+    d = c.shape[1]
+    assert c.dtype == out.dtype == wts.dtype == torch.float32 and c.is_contiguous() and out.is_contiguous()
+    assert tuple(out.shape) == (T, d) and place_of_row.numel() == T * per and wts.is_contiguous()
+    _check(_fn("moe_tc", "odin_moe_combine")(_ptr(c), _ptr(place_of_row), _ptr(wts), c_int(T), c_int(per), c_int(d),
+                                             _ptr(out), _stream()), "moe_combine")
+
+
+def moe_tc_check() -> None:
+    """Raise if a grouped product gave up a bounded wait since the last check (synchronises)."""
+    f = build.load("moe_tc").odin_moe_tc_error
+    f.restype = c_int
+    if f() != 0:
+        raise KernelError("moe_grouped: a device-side wait ran out (pipeline stalled); results are invalid")
+
+
 def gated_lookup(gate: torch.Tensor, kind: str, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, c] = act(gate[t, c]) * table[ids[t], col0 + c]; gate may be [parts, T, n] partial sums."""
     T, n = out.shape

@@ -47,6 +47,9 @@ SWIGLU_FUSED_FROM = int(os.environ.get("ODIN_SWIGLU_FUSED_FROM", "129"))
 # kernel, in tiles of 256 tokens (see Runtime.linear)
 WIDE_CHUNKS_MAX_TOKENS = int(os.environ.get("ODIN_WIDE_CHUNKS_MAX_TOKENS", "1024"))  # measured: faster up to there
 
+# from this many rows (token, choice) on, the experts run as grouped tensor-core products over rows sorted by expert
+MOE_GROUPED_FROM_ROWS = int(os.environ.get("ODIN_MOE_GROUPED_FROM", "256"))
+
 # ring length of a product that shares the SM with a decode attention CTA (see Runtime.linear)
 LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "5"))
 
@@ -223,10 +226,28 @@ class Runtime:
                 wts: torch.Tensor, activation: str) -> torch.Tensor:
         """The chosen experts' gated feed-forwards for every (token, choice): ids / wts [T, per] name each
         choice's expert (-1: none) and weight; w_gate_up [experts, 2 inner, width], w_down [experts, width,
-        inner].  Returns float32 [per, T, width]: slice k holds every token's k-th choice, weighted; partial
-        sums of the update."""
+        inner].  Returns the tokens' update: float32 [per, T, width] partial sums (slice k holds every token's
+        k-th choice, weighted) from the row-by-row kernels, or float32 [T, width] from the grouped products."""
         T, per = ids.shape
         inner, width = w_down.shape[2], w_down.shape[1]
+        if T * per >= MOE_GROUPED_FROM_ROWS and ops.moe_grouped_supported(h, w_gate_up, w_down) and width % 4 == 0:
+            # many rows: sorted by expert and multiplied tile by tile on the tensor cores (a row's weights are read
+            # once per tile of 128 rows instead of once per row)
+            n_e = w_down.shape[0]
+            places = ops.moe_places(T * per, n_e)
+            place_of_row = self.empty(T * per, dtype=torch.int32)
+            row_of_place = self.empty(places, dtype=torch.int32)
+            tile_expert = self.empty(places // 128, dtype=torch.int32)
+            ops.moe_plan(ids, n_e, place_of_row, row_of_place, tile_expert)
+            hs = self.empty(places, h.shape[1])
+            ops.moe_gather(h, row_of_place, per, hs)
+            a = self.empty(places, inner)
+            ops.moe_grouped(hs, w_gate_up, tile_expert, a, activation)
+            c = self.empty(places, width, dtype=torch.float32)
+            ops.moe_grouped(a, w_down, tile_expert, c)
+            y = self.empty(T, width, dtype=torch.float32)
+            ops.moe_combine(c, place_of_row, wts, y)
+            return y
         a = self.empty(T * per, inner)
         ops.moe_gate_up(h, w_gate_up, ids, activation, a)
         y = self.empty(per, T, width, dtype=torch.float32)

@@ -22,7 +22,8 @@ class RoutedExperts(FeedForward):
     uses with weight 1 (a gated feed-forward is a sum over its inner columns) and rides in the same launches;
     any other shared expert runs as a dense gated feed-forward beside them.
 
-    The update comes back as partial sums, one slice per choice, which the next norm adds in order."""
+    The update of few tokens comes back as partial sums, one slice per choice, which the next norm adds in order;
+    with many tokens the rows are sorted by expert and run as grouped tensor-core products (`Runtime.experts`)."""
 
     graph_safe = True
 
@@ -46,7 +47,7 @@ class RoutedExperts(FeedForward):
         n = self.names
         out = [ParamSpec(n["router"], (self.n_experts, self.width))]
         if n.get("router_bias"):
-            out.append(ParamSpec(n["router_bias"], (self.n_experts,), init="logit"))
+            out.append(ParamSpec(n["router_bias"], (self.n_experts,), init="near_zero"))
         for e in range(self.n_experts):
             g, u, d = self._expert_names(e)
             out += [ParamSpec(g, (self.inner, self.width)), ParamSpec(u, (self.inner, self.width)),
@@ -83,7 +84,7 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.stack([t.contiguous() for t in down]).contiguous()
 
     def kernel_groups(self):
-        return {"moe", "elementwise", "rowwise", "gemm_plain"}
+        return {"moe", "moe_tc", "elementwise", "rowwise", "gemm_plain"}
 
     def forward(self, rt, step, h, residual=None):
         T = h.shape[0]

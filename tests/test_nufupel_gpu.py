@@ -577,3 +577,59 @@ def test_attention_kernels_with_a_sink_and_keys_at_the_windows_edge(kernel, H, G
         torch.cuda.synchronize()
         ops.attention_decode_check()
         close(out.reshape(3, H, hd), want[rows], tol)
+
+
+@pytest.mark.parametrize("T,E,top,always,d,ff", [(300, 6, 2, 2, 128, 96), (700, 12, 4, 1, 64, 64), (257, 3, 1, 0, 256, 136),
+                                                 (90, 40, 3, 0, 72, 8)])
+def test_experts_as_grouped_tensor_core_products(T, E, top, always, d, ff):
+    """Many rows: sorted by expert, padded to tiles, multiplied by the tile's own expert on the tensor cores.  Against
+    a loop over tokens and choices; experts without a row, experts with more than a tile of rows, an inner size that
+    is no multiple of the tile; twice with equal bits (the places differ from run to run, the values do not); padding
+    rows; and against the row-by-row kernels."""
+    from odin_infer_b200.csrc import ops
+    from odin_infer_b200.engine import runtime as R
+    torch.manual_seed(T + E)
+    dtype = torch.bfloat16
+    h = torch.randn(T, d, device=DEV).to(dtype)
+    wr = (torch.randn(E, d, device=DEV) * 3 / math.sqrt(d)).to(dtype)
+    wr[E // 2] = 0          # an expert that is chosen by its bias alone ...
+    bias = torch.randn(E, device=DEV)
+    bias[E // 2] = -50.0    # ... never
+    bias[0] = 2.5           # and one that most tokens choose: more than a tile of rows
+    tok_seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+    tok_seq[5] = tok_seq[T - 1] = -1
+    ids = torch.empty(T, top + always, dtype=torch.int32, device=DEV)
+    wts = torch.empty(T, top + always, dtype=torch.float32, device=DEV)
+    ops.moe_router(h, wr, bias, top, always, tok_seq, ids, wts)
+    n_e = E + always
+    wgu = (torch.randn(n_e, 2 * ff, d, device=DEV) / math.sqrt(d)).to(dtype)
+    wd = (torch.randn(n_e, d, ff, device=DEV) / math.sqrt(ff)).to(dtype)
+    rt = R.Runtime(DEV, dtype)
+    old = R.MOE_GROUPED_FROM_ROWS
+    try:
+        R.MOE_GROUPED_FROM_ROWS = 1
+        y1 = rt.experts(h, wgu, wd, ids, wts, "silu")
+        y2 = rt.experts(h, wgu, wd, ids, wts, "silu")
+        g1 = rt.experts(h, wgu, wd, ids, wts, "gelu_tanh")
+        R.MOE_GROUPED_FROM_ROWS = 1 << 30
+        rows = rt.experts(h, wgu, wd, ids, wts, "silu")
+    finally:
+        R.MOE_GROUPED_FROM_ROWS = old
+    torch.cuda.synchronize()
+    ops.moe_tc_check()
+    assert tuple(y1.shape) == (T, d) and tuple(rows.shape) == (top + always, T, d)
+    assert torch.equal(y1, y2)
+    assert (y1[5] == 0).all() and (y1[T - 1] == 0).all()
+    hd_, g_, d_ = h.double().cpu(), wgu.double().cpu(), wd.double().cpu()
+    idc, wtc = ids.cpu(), wts.double().cpu()
+    for act, got in ((P.silu, y1), (P.gelu_tanh, g1)):
+        want = torch.zeros(T, d, dtype=F64)
+        for k in range(top + always):
+            e = idc[:, k].long()
+            ok = e >= 0
+            ee = e.clamp(min=0)
+            a = act(torch.einsum("tfd,td->tf", g_[ee, :ff], hd_)) * torch.einsum("tfd,td->tf", g_[ee, ff:], hd_)
+            a = a.to(torch.bfloat16).double()    # the activations between the two products are bfloat16
+            want += torch.where(ok[:, None], wtc[:, k, None] * torch.einsum("tdf,tf->td", d_[ee], a), torch.zeros(1, dtype=F64))
+        close(got, want, 4e-3)
+    close(rows.sum(0), y1, 4e-3)
