@@ -26,16 +26,26 @@ __device__ __forceinline__ float moe_activate(int act, float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// sum_i w[i] x[i] over a row of n elements: lanes stride the row, the warp adds up; every lane gets the sum
+// sum_i w[i] x[i] over a row of n elements: lanes stride the row four vectors at a time (their loads go out together),
+// the warp adds up; every lane gets the sum.  The order of the additions depends on n alone.
 __device__ __forceinline__ float warp_dot(const float* __restrict__ w, const float* __restrict__ x, int n, int lane) {
     float acc = 0.f;
     if ((n & 3) == 0 && (((uintptr_t)w) & 15) == 0) {
-        for (int i = lane * 4; i < n; i += 128) {
-            const float4 v = *reinterpret_cast<const float4*>(w + i);
-            acc = fmaf(v.x, x[i], acc);
-            acc = fmaf(v.y, x[i + 1], acc);
-            acc = fmaf(v.z, x[i + 2], acc);
-            acc = fmaf(v.w, x[i + 3], acc);
+        for (int i0 = lane * 4; i0 < n; i0 += 512) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i0 + u * 128 < n) v[u] = *reinterpret_cast<const float4*>(w + i0 + u * 128);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * 128;
+                if (i < n) {
+                    acc = fmaf(v[u].x, x[i], acc);
+                    acc = fmaf(v[u].y, x[i + 1], acc);
+                    acc = fmaf(v[u].z, x[i + 2], acc);
+                    acc = fmaf(v[u].w, x[i + 3], acc);
+                }
+            }
         }
     } else {
         for (int i = lane; i < n; i += 32) acc = fmaf(w[i], x[i], acc);
@@ -46,14 +56,23 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ w, const flo
 __device__ __forceinline__ float warp_dot(const bf16* __restrict__ w, const float* __restrict__ x, int n, int lane) {
     float acc = 0.f;
     if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
-        for (int i = lane * 8; i < n; i += 256) {
-            const uint4 v = *reinterpret_cast<const uint4*>(w + i);
-            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+        for (int i0 = lane * 8; i0 < n; i0 += 1024) {
+            uint4 v[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __bfloat1622float2(p[j]);
-                acc = fmaf(f.x, x[i + 2 * j], acc);
-                acc = fmaf(f.y, x[i + 2 * j + 1], acc);
+            for (int u = 0; u < 4; ++u)
+                if (i0 + u * 256 < n) v[u] = *reinterpret_cast<const uint4*>(w + i0 + u * 256);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * 256;
+                if (i < n) {
+                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[u]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __bfloat1622float2(p[j]);
+                        acc = fmaf(f.x, x[i + 2 * j], acc);
+                        acc = fmaf(f.y, x[i + 2 * j + 1], acc);
+                    }
+                }
             }
         }
     } else {
@@ -63,11 +82,13 @@ __device__ __forceinline__ float warp_dot(const bf16* __restrict__ w, const floa
 }
 
 // ------------------------------------------------------------ router
-// One block per token.  ids, wts: [T, top + always].
+// One block per token.  ids, wts: [T, top + always].  logits (optional): W h as a product has left it, float32 [T, E];
+// the block then only adds the bias, chooses and weighs.
 template <typename TH, typename TW>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(1024)
 moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restrict__ w, VecRef bias, int E, int d, int top,
-                  int always, const int* __restrict__ tok_seq, int* __restrict__ ids, float* __restrict__ wts) {
+                  int always, const int* __restrict__ tok_seq, int* __restrict__ ids, float* __restrict__ wts,
+                  const float* __restrict__ logits) {
     extern __shared__ float sm[];
     float* hrow = sm;       // d
     float* z = sm + d;      // E
@@ -82,12 +103,16 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
         }
         return;
     }
-    for (int i = threadIdx.x; i < d; i += blockDim.x) hrow[i] = to_f32(h[(size_t)t * h_stride + i]);
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-    for (int e = warp; e < E; e += n_warps) {
-        const float s = warp_dot(w + (size_t)e * d, hrow, d, lane);
-        if (lane == 0) z[e] = s + (bias.p != nullptr ? bias.at(e) : 0.f);
+    if (logits != nullptr) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) z[e] = logits[(size_t)t * E + e] + (bias.p != nullptr ? bias.at(e) : 0.f);
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) hrow[i] = to_f32(h[(size_t)t * h_stride + i]);
+        __syncthreads();
+        for (int e = warp; e < E; e += n_warps) {
+            const float s = warp_dot(w + (size_t)e * d, hrow, d, lane);
+            if (lane == 0) z[e] = s + (bias.p != nullptr ? bias.at(e) : 0.f);
+        }
     }
     __syncthreads();
     if (warp == 0) {
@@ -127,19 +152,23 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
 
 extern "C" int odin_moe_router(const void* h, int h_dtype, long long h_stride, const void* w, int w_dtype, const void* bias,
                                int bias_dtype, int T, int E, int d, int top, int always, const int* tok_seq, int* ids,
-                               float* wts, void* stream) {
+                               float* wts, const float* logits, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > 32 || top > E || always < 0 || d <= 0) return ODIN_ERR_UNSUPPORTED;
     const size_t smem = (size_t)(d + E) * sizeof(float);
     if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     VecRef bv{bias, bias_dtype == ODIN_BF16};
+    // a warp per expert while the tokens are few (their blocks cannot fill the GPU); four warps a token else
+    int threads = 128;
+    if (logits != nullptr) threads = 32;
+    else if (T <= 64) threads = E >= 32 ? 1024 : E >= 16 ? 512 : E >= 8 ? 256 : 128;
 #define GO(TH, TW)                                                                                                   \
     do {                                                                                                             \
         if (smem > 48 * 1024)                                                                                        \
             cudaFuncSetAttribute(moe_router_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        odin_launch(moe_router_kernel<TH, TW>, dim3(T), dim3(128), smem, s, (const TH*)h, (size_t)h_stride,          \
-                    (const TW*)w, bv, E, d, top, always, tok_seq, ids, wts);                                         \
+        odin_launch(moe_router_kernel<TH, TW>, dim3(T), dim3(threads), smem, s, (const TH*)h, (size_t)h_stride,      \
+                    (const TW*)w, bv, E, d, top, always, tok_seq, ids, wts, logits);                                 \
     } while (0)
     if (h_dtype == ODIN_BF16 && w_dtype == ODIN_BF16) GO(bf16, bf16);
     else if (h_dtype == ODIN_F32 && w_dtype == ODIN_F32) GO(float, float);

@@ -12,8 +12,9 @@
 // A row's values do not depend on its place (each output element is its own sum over K in the order of the K
 // blocks), so the places may be handed out in any order: equal inputs give equal bits whatever the batch.
 // The grouped kernel: one CTA per (column tile, row tile); warp 0 feeds a ring of stages by TMA (128-byte swizzle),
-// one lane of warp 1 issues the MMAs into tensor memory, warps 2..5 read the accumulator back and store.  Two CTAs
-// share an SM, so one's epilogue runs beside the other's products.  Every wait is bounded (tc::mbar_wait).
+// one lane of warp 1 issues the MMAs (128 x 256 each) into tensor memory, warps 2..5 read the accumulator back and
+// store.  With many tiles two CTAs share an SM, so one's epilogue runs beside the other's products; with few, each has
+// a longer ring.  Every wait is bounded (tc::mbar_wait).
 #include <mutex>
 #include <unordered_map>
 
@@ -22,7 +23,7 @@
 namespace {
 
 constexpr int BM = 128;   // sorted rows per tile (MMA M)
-constexpr int BN = 128;   // output columns per tile (MMA N)
+constexpr int BN = 128;   // output columns per accumulator of the gated product (MMA N); the plain product takes 2 BN
 constexpr int BK = 64;    // K elements per stage: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 
@@ -117,18 +118,21 @@ struct GroupedParams {
     int K;
     int rows_per_expert;   // weight rows of one expert in the stacked matrix (DUAL: 2 N, gate rows first)
     int act;
+    int stages;            // length of the ring of stages (2: two CTAs share an SM; 4: few CTAs, each with more in flight)
     const int* tile_expert;
     int* error;
 };
 
-template <bool DUAL>
+// DUAL: two accumulators of BN columns (gate, up), two weight boxes of BN rows a stage.  Plain: one accumulator of
+// 2 BN columns, one weight box of 2 BN rows.  Either way a stage is 48 KB and the CTA holds 256 columns.
 struct GCfg {
-    static constexpr int STAGES = DUAL ? 2 : 3;
+    static constexpr int MAX_STAGES = 4;
     static constexpr int STAGE_A = BM * BK * 2;
-    static constexpr int STAGE_B = BN * BK * 2;
-    static constexpr int STAGE = STAGE_A + (DUAL ? 2 : 1) * STAGE_B;
-    static constexpr int TMEM_COLS = DUAL ? 256 : 128;
-    static constexpr int SMEM = STAGES * STAGE + 1024 + 128;
+    static constexpr int STAGE_B = 2 * BN * BK * 2;
+    static constexpr int STAGE = STAGE_A + STAGE_B;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int HEAD = 1024;  // barriers and flags, before the stages (which start 1024-byte aligned)
+    static constexpr int smem(int stages) { return 1024 + HEAD + stages * STAGE; }
 };
 
 __device__ __forceinline__ float act_gate(int act, float g) {
@@ -140,18 +144,21 @@ __device__ __forceinline__ float act_gate(int act, float g) {
 template <bool DUAL, typename TO>
 __global__ void __launch_bounds__(192)
 moe_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GroupedParams p) {
-    using C = GCfg<DUAL>;
+    using C = GCfg;
+    constexpr int TILE_N = DUAL ? BN : 2 * BN;   // output columns of a tile
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
-    uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_full = empty + C::STAGES;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(base);
+    uint64_t* empty = full + C::MAX_STAGES;
+    uint64_t* acc_full = empty + C::MAX_STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint8_t* smem = base + 1024;   // the stages: 1024-byte aligned for the 128-byte swizzle
+    const uint32_t n_stages = (uint32_t)p.stages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_trigger();
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
+        for (int s = 0; s < C::MAX_STAGES; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
         tc::mbar_init(acc_full, 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
@@ -168,7 +175,7 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const int n_kb = (p.K + BK - 1) / BK;
-    const int w_row0 = e * p.rows_per_expert + tile_n * BN;
+    const int w_row0 = e * p.rows_per_expert + tile_n * TILE_N;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -179,20 +186,26 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 uint8_t* sa = smem + stage * C::STAGE;
                 tc::mbar_expect_tx(&full[stage], C::STAGE);
                 tc::tma_load_2d(sa, &map_a, kb * BK, tile_m * BM, &full[stage]);
-                tc::tma_load_2d(sa + C::STAGE_A, &map_w, kb * BK, w_row0, &full[stage]);
-                if (DUAL) tc::tma_load_2d(sa + C::STAGE_A + C::STAGE_B, &map_w, kb * BK, w_row0 + p.N, &full[stage]);
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                if (DUAL) {   // two boxes of BN rows: the gate rows and, N rows further, the up rows
+                    tc::tma_load_2d(sa + C::STAGE_A, &map_w, kb * BK, w_row0, &full[stage]);
+                    tc::tma_load_2d(sa + C::STAGE_A + C::STAGE_B / 2, &map_w, kb * BK, w_row0 + p.N, &full[stage]);
+                } else {      // one box of 2 BN rows
+                    tc::tma_load_2d(sa + C::STAGE_A, &map_w, kb * BK, w_row0, &full[stage]);
+                }
+                if (++stage == n_stages) { stage = 0; phase ^= 1; }
             }
             if (!ok) {
                 // aborted: let the copies already in flight land before the CTA's memory is released
-                for (uint32_t s2 = 0; s2 < (uint32_t)C::STAGES; ++s2)
+                for (uint32_t s2 = 0; s2 < n_stages; ++s2)
                     for (uint32_t i = 0; i < 4096; ++i)
                         if (tc::mbar_try_wait(&full[s2], 0) || tc::mbar_try_wait(&full[s2], 1)) break;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = tc::make_idesc_bf16(BM, BN);
+            // the gate and up tiles lie one after the other in a stage: one MMA of 2 BN columns covers both
+            // accumulators (DUAL) or the one wide accumulator (plain)
+            constexpr uint32_t idesc = tc::make_idesc_bf16(BM, 2 * BN);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int kb = 0; kb < n_kb; ++kb) {
@@ -204,14 +217,8 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k)   // +32 bytes per K step inside the swizzle row: +2 in 16-byte units
                     tc::umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                if (DUAL) {
-                    const uint64_t db2 = tc::make_smem_desc_sw128(ax + C::STAGE_A + C::STAGE_B);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc::umma_bf16(tmem_base + BN, da + 2 * k, db2 + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                }
                 tc::umma_commit(&empty[stage]);
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                if (++stage == n_stages) { stage = 0; phase ^= 1; }
             }
             if (ok) tc::umma_commit(acc_full);
         }
@@ -222,7 +229,7 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const size_t i = (size_t)tile_m * BM + quarter * 32 + lane;   // the place; every place of a tile exists
             TO* out = reinterpret_cast<TO*>(p.out) + i * p.ldc;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < TILE_N; c0 += 32) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + c0;
                 if (DUAL) {
@@ -236,7 +243,7 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     tc::tmem_ld32(taddr, r);
                     tc::tmem_ld_wait();
                 }
-                const int j0 = tile_n * BN + c0;
+                const int j0 = tile_n * TILE_N + c0;
                 if (j0 < p.N) {
                     const int n = min(32, p.N - j0);
                     if (sizeof(TO) == 4) {
@@ -296,14 +303,14 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// A row-major [rows, K] bfloat16 matrix with row stride ld, read in boxes of 64 (K) x 128 rows, 128-byte swizzle,
-// zeros beyond the edges.
-int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld) {
+// A row-major [rows, K] bfloat16 matrix with row stride ld, read in boxes of 64 (K) x box_rows rows, 128-byte
+// swizzle, zeros beyond the edges.
+int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return ODIN_ERR_UNSUPPORTED;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -321,17 +328,33 @@ int* error_flag() {
     return flag;
 }
 
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <bool DUAL, typename TO>
-int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mw, const GroupedParams& p, int tiles_m, cudaStream_t s) {
-    using C = GCfg<DUAL>;
+int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mw, GroupedParams p, int tiles_m, cudaStream_t s) {
+    using C = GCfg;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<DUAL, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<DUAL, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             C::smem(C::MAX_STAGES));
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)tiles_m);
-    odin_launch(moe_grouped_kernel<DUAL, TO>, grid, dim3(192), (size_t)C::SMEM, s, ma, mw, p);
+    const int tile_n = DUAL ? BN : 2 * BN;
+    const dim3 grid((unsigned)((p.N + tile_n - 1) / tile_n), (unsigned)tiles_m);
+    // Few CTAs (a step of few tokens: the weights stream once, an SM holds one CTA): a ring of four stages, so that
+    // enough is in flight; many CTAs: two stages, and two CTAs share an SM, one's epilogue beside the other's products.
+    // The number of CTAs follows from the shapes alone.
+    p.stages = ((long long)grid.x * grid.y <= 2LL * sm_count()) ? C::MAX_STAGES : 2;
+    odin_launch(moe_grouped_kernel<DUAL, TO>, grid, dim3(192), (size_t)C::smem(p.stages), s, ma, mw, p);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
@@ -385,10 +408,10 @@ extern "C" int odin_moe_grouped(const void* a, long long lda, const void* w, lon
     if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)a) & 15) || (((uintptr_t)w) & 15)) return ODIN_ERR_UNSUPPORTED;
     CUtensorMap ma, mw;
     int rc;
-    if ((rc = make_map(&ma, a, places, K, lda))) return rc;
-    if ((rc = make_map(&mw, w, (long long)n_experts * rows_per_expert, K, ldw))) return rc;
+    if ((rc = make_map(&ma, a, places, K, lda, BM))) return rc;
+    if ((rc = make_map(&mw, w, (long long)n_experts * rows_per_expert, K, ldw, dual ? BN : 2 * BN))) return rc;
     GroupedParams p;
-    p.out = out; p.ldc = ldc; p.N = N; p.K = K; p.rows_per_expert = rows_per_expert; p.act = act;
+    p.out = out; p.ldc = ldc; p.N = N; p.K = K; p.rows_per_expert = rows_per_expert; p.act = act; p.stages = 2;
     p.tile_expert = tile_expert;
     p.error = error_flag();
     cudaStream_t s = (cudaStream_t)stream;

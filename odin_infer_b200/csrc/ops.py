@@ -270,10 +270,10 @@ def softcap(z: torch.Tensor, cap: float) -> None:
 
 
 def moe_router(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: int, always: int,
-               tok_seq: torch.Tensor | None, ids: torch.Tensor, wts: torch.Tensor) -> None:
+               tok_seq: torch.Tensor | None, ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor | None = None) -> None:
     """Per token: logits W h + bias in 32-bit, the `top` largest chosen, weights = softmax over the chosen logits;
     `always` further choices name the experts E, E + 1, ... with weight 1.  ids int32, wts float32: [T, top + always];
-    rows of sequence -1 get expert -1."""
+    rows of sequence -1 get expert -1.  logits: W h where a product has formed it already (float32 [T, E])."""
     T, d = h.shape
     E = w.shape[0]
     assert h.stride(1) == 1 and w.is_contiguous() and w.shape[1] == d
@@ -281,10 +281,12 @@ def moe_router(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top:
     assert tuple(ids.shape) == tuple(wts.shape) == (T, top + always)
     if bias is not None:
         assert bias.numel() == E and bias.is_contiguous()
+    if logits is not None:
+        assert logits.dtype == torch.float32 and logits.is_contiguous() and tuple(logits.shape) == (T, E)
     _check(_fn("moe", "odin_moe_router")(
         _ptr(h), c_int(dtype_code(h.dtype)), c_longlong(h.stride(0)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(bias),
         c_int(dtype_code(bias.dtype) if bias is not None else 0), c_int(T), c_int(E), c_int(d), c_int(top), c_int(always),
-        _ptr(tok_seq), _ptr(ids), _ptr(wts), _stream()), "moe_router")
+        _ptr(tok_seq), _ptr(ids), _ptr(wts), _ptr(logits), _stream()), "moe_router")
 
 
 def moe_gate_up(h: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, kind: str, out: torch.Tensor) -> None:

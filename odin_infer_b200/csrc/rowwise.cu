@@ -450,16 +450,49 @@ sigmoid_gate_kernel(TO* __restrict__ o, size_t o_stride, const TG* __restrict__ 
     }
 }
 
+// Four elements at a time: vd, every row distance and every pointer are that much aligned.
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_vec_kernel(TO* __restrict__ o, size_t o_stride, const TG* __restrict__ gate, int n_split, size_t split_stride,
+                        size_t gate_stride, int per_head, int T, int H, int vd) {
+    pdl_trigger();
+    pdl_wait();
+    const int n4 = H * vd / 4;
+    const long long total = (long long)T * n4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / n4), c = (int)(i % n4) * 4;
+        float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (per_head) {
+            float zh = 0.f;
+            for (int s = 0; s < n_split; ++s) zh += to_f32(gate[(size_t)s * split_stride + (size_t)t * gate_stride + c / vd]);
+            z = make_float4(zh, zh, zh, zh);
+        } else {
+            for (int s = 0; s < n_split; ++s) {
+                const float4 g = ld4(gate + (size_t)s * split_stride + (size_t)t * gate_stride + c);
+                z.x += g.x; z.y += g.y; z.z += g.z; z.w += g.w;
+            }
+        }
+        TO* p = o + (size_t)t * o_stride + c;
+        const float4 v = ld4(p);
+        st4(p, make_float4(v.x / (1.0f + expf(-z.x)), v.y / (1.0f + expf(-z.y)), v.z / (1.0f + expf(-z.z)), v.w / (1.0f + expf(-z.w))));
+    }
+}
+
 extern "C" int odin_sigmoid_gate(void* o, int o_dtype, long long o_stride, const void* gate, int gate_dtype, int n_split,
                                  long long split_stride, long long gate_stride, int per_head, int T, int H, int vd,
                                  void* stream) {
     if (T <= 0 || H <= 0 || vd <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const long long total = (long long)T * H * vd;
+    const bool vec = (vd % 4 == 0) && (o_stride % 4 == 0) && ((((uintptr_t)o) & 15) == 0) &&
+                     (per_head || ((gate_stride % 4 == 0) && (split_stride % 4 == 0) && ((((uintptr_t)gate) & 15) == 0)));
+    const long long total = (long long)T * H * vd / (vec ? 4 : 1);
     const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
 #define GO(TG, TO)                                                                                                   \
-    odin_launch(sigmoid_gate_kernel<TG, TO>, dim3(blocks), dim3(256), 0, s, (TO*)o, (size_t)o_stride, (const TG*)gate, \
-                n_split, (size_t)split_stride, (size_t)gate_stride, per_head, T, H, vd)
+    do {                                                                                                             \
+        auto kern = vec ? sigmoid_gate_vec_kernel<TG, TO> : sigmoid_gate_kernel<TG, TO>;                             \
+        odin_launch(kern, dim3(blocks), dim3(256), 0, s, (TO*)o, (size_t)o_stride, (const TG*)gate, n_split,         \
+                    (size_t)split_stride, (size_t)gate_stride, per_head, T, H, vd);                                  \
+    } while (0)
     if (gate_dtype == ODIN_F32 && o_dtype == ODIN_F32) GO(float, float);
     else if (gate_dtype == ODIN_F32 && o_dtype == ODIN_BF16) GO(float, bf16);
     else if (gate_dtype == ODIN_BF16 && o_dtype == ODIN_BF16) GO(bf16, bf16);

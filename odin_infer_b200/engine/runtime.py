@@ -48,7 +48,7 @@ SWIGLU_FUSED_FROM = int(os.environ.get("ODIN_SWIGLU_FUSED_FROM", "129"))
 WIDE_CHUNKS_MAX_TOKENS = int(os.environ.get("ODIN_WIDE_CHUNKS_MAX_TOKENS", "1024"))  # measured: faster up to there
 
 # from this many rows (token, choice) on, the experts run as grouped tensor-core products over rows sorted by expert
-MOE_GROUPED_FROM_ROWS = int(os.environ.get("ODIN_MOE_GROUPED_FROM", "256"))
+MOE_GROUPED_FROM_ROWS = int(os.environ.get("ODIN_MOE_GROUPED_FROM", "64"))
 
 # ring length of a product that shares the SM with a decode attention CTA (see Runtime.linear)
 LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "5"))

@@ -91,7 +91,12 @@ class RoutedExperts(FeedForward):
         per = self.top + self.shared_as_experts
         ids = rt.empty(T, per, dtype=torch.int32)
         wts = rt.empty(T, per, dtype=torch.float32)
-        ops.moe_router(h, self.w_router, self.b_router, self.top, self.shared_as_experts, step.tok_seq, ids, wts)
+        logits = None
+        if T > 64 and rt.dtype == torch.bfloat16 and ops.gemm_tc_supported(h, self.w_router):
+            # many tokens: the logits as a tensor-core product (bfloat16 factors, 32-bit sums); the 32-bit engine keeps
+            # the one kernel whatever the number of tokens, so that a token's logits are the same bits in every cut
+            logits = rt.linear(h, self.w_router, out_dtype=torch.float32)
+        ops.moe_router(h, self.w_router, self.b_router, self.top, self.shared_as_experts, step.tok_seq, ids, wts, logits)
         y = rt.experts(h, self.w_gate_up, self.w_down, ids, wts, self.activation)
         if self.ws_gate_up is None:
             return y
