@@ -586,8 +586,10 @@ def nufupel_kernels(z: dict, T: int, peaks: dict) -> dict:
     ids = torch.empty(T, top + always, dtype=torch.int32, device=dev)
     wts = torch.empty(T, top + always, dtype=torch.float32, device=dev)
     seq = torch.zeros(T, dtype=torch.int32, device=dev)
-    note("router (logits, choice, weights)", timed(lambda: ops.moe_router(h, wr, None, top, always, seq, ids, wts), flush),
-         nbytes=T * d * 2 + E * d * 2)
+    def route():   # as the feed-forward part does it: the logits of many tokens as a tensor-core product
+        lg = rt.linear(h, wr, out_dtype=torch.float32) if T > 64 else None
+        ops.moe_router(h, wr, None, top, always, seq, ids, wts, lg)
+    note("router (logits, choice, weights)", timed(route, flush), nbytes=T * d * 2 + E * d * 2)
     n_e = E + always
     wg = (torch.randn(n_e, 2 * eff, d, device=dev) * 0.02).to(bf)
     wd = (torch.randn(n_e, d, eff, device=dev) * 0.02).to(bf)

@@ -93,13 +93,16 @@ class NufupelConfig(ModelConfig):
         for i, entry in enumerate(raw_layers):
             layers.append(cls._layer(r, i, entry if isinstance(entry, dict) else {}))
         for i, l in enumerate(layers):
-            j = l.weights_of
-            if j is not None:
-                ok = 0 <= j < len(layers) and j != i and layers[j].weights_of is None
-                r.require(ok, f"layer {i}: weights_of ({j}) must name another layer that has tensors of its own")
+            j, hops = l.weights_of, 0
+            while j is not None and 0 <= j < len(layers) and layers[j].weights_of is not None and hops < len(layers):
+                j, hops = layers[j].weights_of, hops + 1     # a layer that borrows from a borrower uses the lender's
+            if l.weights_of is not None:
+                ok = j is not None and 0 <= j < len(layers) and j != i and layers[j].weights_of is None
+                r.require(ok, f"layer {i}: weights_of ({l.weights_of}) must lead to another layer that has tensors of its own")
                 if ok:
                     r.require(dataclasses.replace(l, weights_of=None) == layers[j],
                               f"layer {i}: its entry differs from that of layer {j}, whose weights it uses")
+                    layers[i] = dataclasses.replace(l, weights_of=j)
         r.finish()
         return cls(architecture=str(raw.get("architecture", "Nufupel")), vocab=vocab, width=width, norm_eps=eps,
                    embedding_scale=scale, logit_softcap=cap, layers=tuple(layers))
