@@ -123,7 +123,9 @@ class Engine:
     def summary(self) -> str:
         """One line at load, as the reference prints (infer/model.odin:228-241)."""
         c = self.config
-        return (f"odin_infer_b200: {c.architecture} {type(c).__name__} layers={len(self.spec.layers)} "
+        runs, own = len(self.spec.schedule), len(self.spec.layers)
+        layers = f"{runs}" if runs == own else f"{runs} ({own} with weights of their own)"
+        return (f"odin_infer_b200: {c.architecture} {type(c).__name__} layers={layers} "
                 f"width={self.spec.width} vocab={self.vocab_size} ctx={self.max_ctx} dtype={self.opts.dtype} "
                 f"weights={self.weight_bytes / 2**30:.2f} GiB cache={self.cache_bytes / 2**20:.1f} MiB "
                 f"({self.cache.n_pages} pages of {PAGE} tokens, {len(self.cache.groups)} group(s), "

@@ -48,7 +48,9 @@ SWIGLU_FUSED_FROM = int(os.environ.get("ODIN_SWIGLU_FUSED_FROM", "129"))
 WIDE_CHUNKS_MAX_TOKENS = int(os.environ.get("ODIN_WIDE_CHUNKS_MAX_TOKENS", "1024"))  # measured: faster up to there
 
 # from this many rows (token, choice) on, the experts run as grouped tensor-core products over rows sorted by expert
-MOE_GROUPED_FROM_ROWS = int(os.environ.get("ODIN_MOE_GROUPED_FROM", "64"))
+# (measured on whole decode steps at widths 2,048 and 4,096: at 48 and 64 rows the grouped products' step is 9 and 11 %
+# shorter than the row kernels', although it launches three kernels more; at 192 rows half as long)
+MOE_GROUPED_FROM_ROWS = int(os.environ.get("ODIN_MOE_GROUPED_FROM", "32"))
 
 # ring length of a product that shares the SM with a decode attention CTA (see Runtime.linear)
 LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "5"))
@@ -230,10 +232,7 @@ class Runtime:
         k-th choice, weighted) from the row-by-row kernels, or float32 [T, width] from the grouped products."""
         T, per = ids.shape
         inner, width = w_down.shape[2], w_down.shape[1]
-        # grouped from a few rows per expert on (measured at widths 2,048 and 4,096: equal at ~1.5 rows per expert,
-        # five times faster at eight)
-        if (T * per >= max(MOE_GROUPED_FROM_ROWS, 2 * w_down.shape[0]) and ops.moe_grouped_supported(h, w_gate_up, w_down)
-                and width % 4 == 0):
+        if T * per >= MOE_GROUPED_FROM_ROWS and ops.moe_grouped_supported(h, w_gate_up, w_down) and width % 4 == 0:
             # many rows: sorted by expert and multiplied tile by tile on the tensor cores (a row's weights are read
             # once per tile of 128 rows instead of once per row)
             n_e = w_down.shape[0]

@@ -124,7 +124,10 @@ class GQAttention(Mixer):
             return []
         out, hd, group = [], self.hd, self.n_q // self.n_kv
         rot = self.pe.rotation() if self.pe is not None else None
-        if not ops.attention_prefill_supported(hd):
+        if self.vd != hd:
+            out.append(f"attention: value heads of {self.vd} beside keys of {hd}: prompts and decoding run the CUDA-core "
+                       "attention kernel (the tensor-core kernels take value heads of the keys' size)")
+        elif not ops.attention_prefill_supported(hd):
             out.append(f"attention: head_dim {hd} is not 64 or 128: prompts run the CUDA-core attention kernel "
                        "(one warp per token and head), far slower than the tensor-core one")
         if not ops.attention_decode_supported(hd):

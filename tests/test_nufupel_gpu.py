@@ -473,7 +473,13 @@ def test_router_and_experts(dtype, tol, E, top, always, d, ff):
     n_e = E + always
     wgu = (torch.randn(n_e, 2 * ff, d, device=DEV) / math.sqrt(d)).to(dtype)
     wd = (torch.randn(n_e, d, ff, device=DEV) / math.sqrt(ff)).to(dtype)
-    y = Runtime(DEV, dtype).experts(h, wgu, wd, ids, wts, "silu")
+    from odin_infer_b200.engine import runtime as R
+    old = R.MOE_GROUPED_FROM_ROWS
+    try:
+        R.MOE_GROUPED_FROM_ROWS = 1 << 30     # the row-by-row kernels (the grouped products have a test of their own)
+        y = Runtime(DEV, dtype).experts(h, wgu, wd, ids, wts, "silu")
+    finally:
+        R.MOE_GROUPED_FROM_ROWS = old
     assert tuple(y.shape) == (top + always, T, d)
     want = torch.zeros(T, d, dtype=F64)
     hd_, g_, d_ = h.double().cpu(), wgu.double().cpu(), wd.double().cpu()
