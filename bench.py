@@ -502,7 +502,7 @@ def nufupel_config(z: dict) -> dict:
     ff = z["top"] * z["eff"] + z["shared"]
     base = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5,
             "mask": {"size": z["window"]}}
-    rot = {"dims": z["hd"] // 2, "base": 250000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}
+    rot = {"dims": z["hd"] // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
     moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared"]}}
     layers = []
     for i in range(z["layers"]):

@@ -118,13 +118,14 @@ def test_plain_window_by_perturbation_and_sink_by_its_limits():
 
 
 def test_plain_rotation_and_stretched_frequencies():
-    f = P.stretched_frequencies(32, 250000.0, {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048})
-    plain = P.stretched_frequencies(32, 250000.0, None)
-    assert torch.allclose(plain, torch.tensor([250000.0 ** (-2 * i / 32) for i in range(16)], dtype=F64))
+    f = P.stretched_frequencies(40, 70000.0, {"factor": 5.0, "low": 2.0, "high": 6.0, "original": 3000})
+    plain = P.stretched_frequencies(40, 70000.0, None)
+    assert torch.allclose(plain, torch.tensor([70000.0 ** (-2 * i / 40) for i in range(20)], dtype=F64))
     wavelength = 2 * math.pi / plain
-    assert torch.equal(f[wavelength < 512], plain[wavelength < 512]) and torch.allclose(f[wavelength > 2048], plain[wavelength > 2048] / 8)
-    mid = (wavelength >= 512) & (wavelength <= 2048)
-    assert mid.any() and ((f[mid] < plain[mid]) & (f[mid] > plain[mid] / 8)).all()
+    assert torch.equal(f[wavelength < 500], plain[wavelength < 500]) and torch.allclose(f[wavelength > 1500], plain[wavelength > 1500] / 5)
+    assert (wavelength < 500).any() and (wavelength > 1500).any()
+    mid = (wavelength >= 500) & (wavelength <= 1500)
+    assert mid.any() and ((f[mid] < plain[mid]) & (f[mid] > plain[mid] / 5)).all()
     # a rotation keeps lengths, leaves the tail alone, and scores depend on the distance of the positions only
     torch.manual_seed(1)
     t = torch.randn(6, 2, 12, dtype=F64)

@@ -68,10 +68,10 @@ ODD = {"architecture": "Nufupel", "vocab": 97, "width": 100, "norm": {"eps": 1e-
                   layer("attention", {"heads": 1, "dim": 20}, moe(3, 3, 28), weights_of=0)]}
 # FAST: the head sizes of the tensor-core attention kernels, windows across several pages, widths the tensor-core
 # products take
-_F1 = layer("attention", mixer(4, 2, 64, 64, 100, 0.125), moe(8, 4, 64, 128))
+_F1 = layer("attention", mixer(4, 2, 64, 64, 100, 0.11), moe(8, 3, 80, 160))
 FAST = {"architecture": "Nufupel", "vocab": 512, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 11.3},
         "logit_softcap": 8.0,
-        "layers": [layer("attention_2", mixer(4, 1, 128, 128, 300, 0.088, {"dims": 64, "base": 25000.0, "scaling": STRETCH}), dense(256)),
+        "layers": [layer("attention_2", mixer(4, 1, 128, 128, 300, 0.088, {"dims": 64, "base": 25000.0, "scaling": STRETCH}), dense(384)),
                    _F1, dict(_F1, weights_of=1),
                    layer("attention_2", mixer(8, 2, 64, 64, 70, 0.125, {"dims": 32, "base": 1e4}), moe(4, 2, 128)),
                    dict(_F1, weights_of=1)]}
@@ -407,7 +407,7 @@ def test_stretched_frequencies_have_all_three_branches():
     """Frequencies kept, divided and blended: against the plain formula, with constants under which each branch holds
     some of the pairs; the tables' angles are 32-bit products of position and frequency."""
     from odin_infer_b200.parts.position import RotaryEncoding
-    for dims, base, sc in ((32, 250000.0, {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}),
+    for dims, base, sc in ((40, 70000.0, {"factor": 5.0, "low": 2.0, "high": 6.0, "original": 3000}),
                            (16, 5000.0, STRETCH), (48, 1e4, None), (2, 10.0, {"factor": 2.0, "low": 0.5, "high": 8.0, "original": 7})):
         pe = RotaryEncoding(dims, base, sc, precise=True)
         ref = P.stretched_frequencies(dims, base, sc)
@@ -417,7 +417,7 @@ def test_stretched_frequencies_have_all_three_branches():
             plain = P.stretched_frequencies(dims, base, None)
             ratio = (ref / plain).numpy()
             assert (ratio == 1.0).any() and np.isclose(ratio, 1.0 / sc["factor"]).any()
-            assert ((ratio < 0.999) & (ratio > 1.001 / sc["factor"])).any() or dims == 32
+            assert ((ratio < 0.999) & (ratio > 1.001 / sc["factor"])).any()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -447,7 +447,7 @@ def test_gates_activations_and_the_cap(dtype):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("E,top,always,d,ff", [(6, 2, 2, 96, 48), (3, 3, 0, 100, 28), (12, 4, 1, 64, 16), (40, 1, 0, 72, 8)])
+@pytest.mark.parametrize("E,top,always,d,ff", [(6, 2, 2, 96, 48), (3, 3, 0, 100, 28), (10, 3, 1, 64, 16), (40, 1, 0, 72, 8)])
 def test_router_and_experts(dtype, tol, E, top, always, d, ff):
     """The router's choices and weights against a sort of the plain logits (logits made distinct by construction),
     padding rows, and the experts' update against a loop over tokens and choices."""
@@ -524,7 +524,7 @@ def _paged(k, v, n_pages_extra=3, seed=0):
 
 @pytest.mark.parametrize("kernel", ["plain32", "plain16", "decode", "prefill"])
 @pytest.mark.parametrize("H,G,hd,window,n", [(4, 2, 64, 100, 333), (2, 1, 128, 70, 200), (4, 4, 64, 64, 130), (8, 2, 64, 300, 140),
-                                            (6, 3, 96, 40, 150), (3, 1, 32, 1, 70)])
+                                            (6, 2, 80, 44, 150), (3, 1, 32, 1, 70)])
 def test_attention_kernels_with_a_sink_and_keys_at_the_windows_edge(kernel, H, G, hd, window, n):
     """One loud key is planted just inside the last query's window and one just outside it (and at a page's border);
     the sinks are loud enough to take a fifth to a half of the denominator.  Every kernel that serves the mixers
@@ -585,7 +585,7 @@ def test_attention_kernels_with_a_sink_and_keys_at_the_windows_edge(kernel, H, G
         close(out.reshape(3, H, hd), want[rows], tol)
 
 
-@pytest.mark.parametrize("T,E,top,always,d,ff", [(300, 6, 2, 2, 128, 96), (700, 12, 4, 1, 64, 64), (257, 3, 1, 0, 256, 136),
+@pytest.mark.parametrize("T,E,top,always,d,ff", [(300, 6, 2, 2, 128, 96), (700, 10, 3, 1, 64, 64), (257, 3, 1, 0, 256, 136),
                                                  (90, 40, 3, 0, 72, 8)])
 def test_experts_as_grouped_tensor_core_products(T, E, top, always, d, ff):
     """Many rows: sorted by expert, padded to tiles, multiplied by the tile's own expert on the tensor cores.  Against
