@@ -45,8 +45,20 @@ moe_plan_kernel(const int* __restrict__ ids, int rows, int n_experts, int* __res
     pdl_wait();
     for (int i = threadIdx.x; i < places_cap; i += blockDim.x) row_of_place[i] = -1;
     for (int i = threadIdx.x; i < places_cap / BM; i += blockDim.x) tile_expert[i] = -1;
+    // a thread's rows are loaded together (a loop of load, atomic, load, ... is a chain of memory latencies); rows
+    // beyond PLAN_HELD per thread are read again in the second pass
+    constexpr int PLAN_HELD = 16;
+    int held[PLAN_HELD];
+#pragma unroll
+    for (int k = 0; k < PLAN_HELD; ++k) {
+        const int r = threadIdx.x + k * 1024;
+        held[k] = r < rows ? ids[r] : -1;
+    }
     __syncthreads();
-    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+#pragma unroll
+    for (int k = 0; k < PLAN_HELD; ++k)
+        if (held[k] >= 0 && held[k] < n_experts) atomicAdd(&count[held[k]], 1);
+    for (int r = threadIdx.x + PLAN_HELD * 1024; r < rows; r += 1024) {
         const int e = ids[r];
         if (e >= 0 && e < n_experts) atomicAdd(&count[e], 1);
     }
@@ -61,7 +73,20 @@ moe_plan_kernel(const int* __restrict__ ids, int rows, int n_experts, int* __res
     __syncthreads();
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
         for (int t = first[e] / BM; t < (first[e] + count[e] + BM - 1) / BM; ++t) tile_expert[t] = e;
-    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+#pragma unroll
+    for (int k = 0; k < PLAN_HELD; ++k) {
+        const int r = threadIdx.x + k * 1024;
+        if (r < rows) {
+            const int e = held[k];
+            int place = -1;
+            if (e >= 0 && e < n_experts) {
+                place = first[e] + atomicAdd(&cursor[e], 1);
+                row_of_place[place] = r;
+            }
+            place_of_row[r] = place;
+        }
+    }
+    for (int r = threadIdx.x + PLAN_HELD * 1024; r < rows; r += 1024) {
         const int e = ids[r];
         int place = -1;
         if (e >= 0 && e < n_experts) {
@@ -73,21 +98,26 @@ moe_plan_kernel(const int* __restrict__ ids, int rows, int n_experts, int* __res
 }
 
 // ------------------------------------------------------------------------------------------------ gather
+// A block takes GATHER_PLACES places; their row numbers, then their rows' loads go out together.
+constexpr int GATHER_PLACES = 4;
 __global__ void __launch_bounds__(256)
-moe_gather_kernel(const bf16* __restrict__ h, size_t h_stride, const int* __restrict__ row_of_place, int per, int d,
+moe_gather_kernel(const bf16* __restrict__ h, size_t h_stride, const int* __restrict__ row_of_place, int places, int per, int d,
                   bf16* __restrict__ out) {
     pdl_trigger();
     pdl_wait();
-    const int place = blockIdx.x;
-    const int r = row_of_place[place];
-    bf16* o = out + (size_t)place * d;
-    if (r < 0) {
-        for (int i = threadIdx.x * 8; i < d; i += blockDim.x * 8) *reinterpret_cast<uint4*>(o + i) = make_uint4(0, 0, 0, 0);
-        return;
+    const int p0 = blockIdx.x * GATHER_PLACES;
+    int r[GATHER_PLACES];
+#pragma unroll
+    for (int k = 0; k < GATHER_PLACES; ++k) r[k] = (p0 + k < places) ? row_of_place[p0 + k] : -2;
+    for (int i = threadIdx.x * 8; i < d; i += blockDim.x * 8) {
+        uint4 v[GATHER_PLACES];
+#pragma unroll
+        for (int k = 0; k < GATHER_PLACES; ++k)
+            v[k] = r[k] >= 0 ? *reinterpret_cast<const uint4*>(h + (size_t)(r[k] / per) * h_stride + i) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int k = 0; k < GATHER_PLACES; ++k)
+            if (r[k] != -2) *reinterpret_cast<uint4*>(out + (size_t)(p0 + k) * d + i) = v[k];
     }
-    const bf16* src = h + (size_t)(r / per) * h_stride;
-    for (int i = threadIdx.x * 8; i < d; i += blockDim.x * 8)
-        *reinterpret_cast<uint4*>(o + i) = *reinterpret_cast<const uint4*>(src + i);
 }
 
 // ------------------------------------------------------------------------------------------------ combine
@@ -382,8 +412,8 @@ extern "C" int odin_moe_gather(const void* h, long long h_stride, const int* row
                                void* stream) {
     if (places <= 0) return 0;
     if (d % 8 != 0 || h_stride % 8 != 0 || ((((uintptr_t)h) | ((uintptr_t)out)) & 15) != 0) return ODIN_ERR_UNSUPPORTED;
-    odin_launch(moe_gather_kernel, dim3(places), dim3(256), 0, (cudaStream_t)stream, (const bf16*)h, (size_t)h_stride,
-                row_of_place, per, d, (bf16*)out);
+    odin_launch(moe_gather_kernel, dim3((places + GATHER_PLACES - 1) / GATHER_PLACES), dim3(256), 0, (cudaStream_t)stream,
+                (const bf16*)h, (size_t)h_stride, row_of_place, places, per, d, (bf16*)out);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
