@@ -157,7 +157,7 @@ def requests_for(raw, lengths, seed=0):
 # In bfloat16 a router's close call may fall the other way than in the plain implementation (the two differ by
 # rounding in what the router reads); the token's update then differs by one expert's share (all of the experts'
 # update where a token uses one expert), and later tokens see it through attention.  The serving engine is therefore
-# judged position by position: the median far inside the tolerance, one position in ten outside it at most, none
+# assessed position by position: the median far inside the tolerance, one position in ten outside it at most, none
 # wild (a token's logits after another expert are a different but ordinary row).  Every kernel alone is held to its
 # tolerance in bfloat16 further down, with choices that are no close calls.  The 32-bit
 # engine, whose router reads what the plain one reads to six digits, is held to the tolerance at every position.
