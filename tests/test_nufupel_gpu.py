@@ -274,6 +274,19 @@ def test_long_decoding(folders, name, dtype):
     engine.destroy()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt(folders, dtype):
+    """A prompt of 1,100 tokens whole, and with its last 40 tokens one by one: windows many pages back from the start, block
+    tables of 18 pages of which a window keeps two to six, experts with several tiles of rows each."""
+    raw = CONFIGS["fast"][0]
+    reqs = requests_for(raw, [1100], seed=70)
+    engine = engine_for(folders["fast"], dtype, max_tokens=2048, max_ctx=1280)
+    for recs in (traces.whole(reqs), traces.tail_one_by_one(reqs, tail=40)):
+        check_rows(traces.collect(recs, replay(engine, recs)), folders["fast"], reqs, dtype)
+    engine.cache.check()
+    engine.destroy()
+
+
 def test_window_groups_keep_a_cache_line_per_run_and_give_pages_back(folders):
     """A layer that runs several times keeps a line per run in one group; a windowed group holds only the pages
     that its window still reaches."""
@@ -524,7 +537,8 @@ def _paged(k, v, n_pages_extra=3, seed=0):
 
 @pytest.mark.parametrize("kernel", ["plain32", "plain16", "decode", "prefill"])
 @pytest.mark.parametrize("H,G,hd,window,n", [(4, 2, 64, 100, 333), (2, 1, 128, 70, 200), (4, 4, 64, 64, 130), (8, 2, 64, 300, 140),
-                                            (6, 2, 80, 44, 150), (3, 1, 32, 1, 70)])
+                                            (6, 2, 80, 44, 150), (3, 1, 32, 1, 70), (4, 2, 64, 3, 200), (4, 2, 64, 65, 200), (2, 2, 128, 128, 300),
+                                            (4, 1, 128, 1, 140), (4, 2, 64, 129, 450)])
 def test_attention_kernels_with_a_sink_and_keys_at_the_windows_edge(kernel, H, G, hd, window, n):
     """One loud key is planted just inside the last query's window and one just outside it (and at a page's border);
     the sinks are loud enough to take a fifth to a half of the denominator.  Every kernel that serves the mixers
